@@ -1,0 +1,148 @@
+"""ctypes bindings of the C ABI declared in include/ahpc.h.
+
+Python is the test and benchmark harness here, not the product: every function below forwards to
+the native library, and the library has no CPU path.  Loading fails loudly if the library has not
+been built (python -m attention_b200.build).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+F32, F16, BF16 = 0, 1, 2
+LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC = 0, 1, 2
+
+STATUS_NAMES = {
+    0: "SUCCESS", 1: "INVALID_INPUT", 2: "INVALID_PARAMETERS", 3: "MEMORY_ALLOCATION_FAILED",
+    4: "COMPUTATION_FAILED", 5: "BACKEND_NOT_AVAILABLE", 6: "UNSUPPORTED_OPERATION", 7: "INTERNAL_ERROR",
+}
+
+# Every symbol include/ahpc.h declares; the CPU test-suite checks the library exports each one.
+EXPORTED_SYMBOLS = [
+    "ahpc_version", "ahpc_last_error_string", "ahpc_device_count", "ahpc_get_device_info",
+    "ahpc_fa_strides", "ahpc_fa_fwd", "ahpc_fa_workspace_bytes", "ahpc_fa_select_kernel",
+    "ahpc_pool_create", "ahpc_pool_destroy", "ahpc_pool_seq_create", "ahpc_pool_seq_destroy",
+    "ahpc_pool_seq_truncate", "ahpc_pool_seq_fork", "ahpc_pool_append", "ahpc_pool_gather",
+    "ahpc_pool_seq_len", "ahpc_pool_seq_pages", "ahpc_pool_free_pages", "ahpc_pool_page_bytes",
+    "ahpc_pool_live_seqs", "ahpc_pool_read_block_table", "ahpc_pool_read_seq_lens",
+    "ahpc_pool_read_refcounts", "ahpc_pool_read_free_ring", "ahpc_pool_read_error_flag",
+    "ahpc_paged_decode", "ahpc_paged_decode_scratch_bytes", "ahpc_shard_range",
+]
+
+
+class AhpcError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+
+
+class FaArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("mask", C.c_void_p), ("lse", C.c_void_p),
+        ("dtype", C.c_int32), ("batch", C.c_int32), ("heads", C.c_int32), ("seq_q", C.c_int32),
+        ("seq_kv", C.c_int32), ("head_dim", C.c_int32),
+        ("q_strides", C.c_int64 * 4), ("k_strides", C.c_int64 * 4), ("v_strides", C.c_int64 * 4),
+        ("o_strides", C.c_int64 * 4),
+        ("scale", C.c_float), ("causal", C.c_int32), ("kernel", C.c_int32), ("device", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
+class PoolConfig(C.Structure):
+    _fields_ = [
+        ("device", C.c_int32), ("dtype", C.c_int32), ("num_pages", C.c_int32), ("page_size", C.c_int32),
+        ("heads", C.c_int32), ("head_dim", C.c_int32), ("max_seqs", C.c_int32), ("max_pages_per_seq", C.c_int32),
+        ("free_order", C.POINTER(C.c_int32)),
+    ]
+
+
+class DecodeArgs(C.Structure):
+    _fields_ = [
+        ("pool", C.c_void_p), ("seqs", C.POINTER(C.c_int32)), ("n_seqs", C.c_int32),
+        ("q", C.c_void_p), ("out", C.c_void_p), ("qo_dtype", C.c_int32), ("scale", C.c_float),
+        ("split_tokens", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [
+        ("name", C.c_char * 256), ("total_memory_bytes", C.c_uint64), ("cc_major", C.c_int32),
+        ("cc_minor", C.c_int32), ("sm_count", C.c_int32), ("max_threads_per_block", C.c_int32),
+        ("max_shared_memory_per_block", C.c_uint64), ("driver_version", C.c_int32), ("runtime_version", C.c_int32),
+    ]
+
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.LIB_PATH
+
+
+def lib() -> C.CDLL:
+    """The loaded native library.  Raises if it is missing: there is no fallback."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: build it with `python -m attention_b200.build` (needs nvcc)")
+    L = C.CDLL(path)
+    i32, i64, vp = C.c_int32, C.c_int64, C.c_void_p
+    pi32 = C.POINTER(C.c_int32)
+    L.ahpc_version.restype = C.c_char_p
+    L.ahpc_last_error_string.restype = C.c_char_p
+    L.ahpc_device_count.restype = i32
+    L.ahpc_get_device_info.argtypes = [i32, C.POINTER(DeviceInfo)]
+    L.ahpc_fa_strides.argtypes = [i32, i64, i64, i64, i64, C.POINTER(C.c_int64 * 4)]
+    L.ahpc_fa_fwd.argtypes = [C.POINTER(FaArgs)]
+    L.ahpc_fa_select_kernel.argtypes = [C.POINTER(FaArgs)]
+    L.ahpc_fa_workspace_bytes.argtypes = [i32, i64, i64, i64, i64, i64, i32]
+    L.ahpc_fa_workspace_bytes.restype = C.c_size_t
+    L.ahpc_pool_create.argtypes = [C.POINTER(vp), C.POINTER(PoolConfig)]
+    L.ahpc_pool_destroy.argtypes = [vp]
+    L.ahpc_pool_seq_create.argtypes = [vp, pi32]
+    L.ahpc_pool_seq_destroy.argtypes = [vp, i32, vp]
+    L.ahpc_pool_seq_truncate.argtypes = [vp, i32, i32, vp]
+    L.ahpc_pool_seq_fork.argtypes = [vp, i32, i32, pi32, vp]
+    L.ahpc_pool_append.argtypes = [vp, pi32, pi32, i32, vp, vp, i32, vp]
+    L.ahpc_pool_gather.argtypes = [vp, i32, i32, i32, vp, vp, i32, vp]
+    L.ahpc_pool_seq_len.argtypes = [vp, i32]
+    L.ahpc_pool_seq_pages.argtypes = [vp, i32]
+    L.ahpc_pool_free_pages.argtypes = [vp]
+    L.ahpc_pool_free_pages.restype = i64
+    L.ahpc_pool_page_bytes.argtypes = [vp]
+    L.ahpc_pool_page_bytes.restype = i64
+    L.ahpc_pool_live_seqs.argtypes = [vp]
+    L.ahpc_pool_read_block_table.argtypes = [vp, i32, pi32, i32, vp]
+    L.ahpc_pool_read_seq_lens.argtypes = [vp, pi32, i32, vp]
+    L.ahpc_pool_read_refcounts.argtypes = [vp, pi32, i32, vp]
+    L.ahpc_pool_read_free_ring.argtypes = [vp, pi32, i32, C.POINTER(i64), vp]
+    L.ahpc_pool_read_error_flag.argtypes = [vp, pi32, vp]
+    L.ahpc_paged_decode.argtypes = [C.POINTER(DecodeArgs)]
+    L.ahpc_paged_decode_scratch_bytes.argtypes = [vp, i32, i32, i32]
+    L.ahpc_paged_decode_scratch_bytes.restype = C.c_size_t
+    L.ahpc_shard_range.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]
+    _lib = L
+    return L
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise AhpcError(status, lib().ahpc_last_error_string().decode())
+
+
+def shard_range(units: int, world: int, rank: int) -> tuple[int, int]:
+    b, e = C.c_int64(), C.c_int64()
+    check(lib().ahpc_shard_range(units, world, rank, C.byref(b), C.byref(e)))
+    return b.value, e.value
+
+
+def fa_strides(layout: int, B: int, H: int, S: int, D: int) -> tuple[int, int, int, int]:
+    st = (C.c_int64 * 4)()
+    check(lib().ahpc_fa_strides(layout, B, H, S, D, C.byref(st)))
+    return tuple(st)

@@ -1,0 +1,121 @@
+"""In-tree build of the native library (nvcc, sm_100a only).
+
+    python -m attention_b200.build            # build what is out of date
+    python -m attention_b200.build --force
+
+Produces attention_b200/lib/libahpc_b200.so: the C ABI of include/ahpc.h, the CUDA kernels behind
+it and the C++ host surface (attention_hpc::BackendFactory, FlashAttention, PagedAttention) that
+sits on top of the C ABI.  Also builds tests/cpp/test_surface, the C++ surface test binary, when
+its source is present.  nvcc cross-compiles without a GPU.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG)
+CSRC = os.path.join(PKG, "csrc")
+LIB_DIR = os.path.join(PKG, "lib")
+OBJ_DIR = os.path.join(PKG, "lib", "obj")
+LIB_PATH = os.path.join(LIB_DIR, "libahpc_b200.so")
+INCLUDES = [os.path.join(ROOT, "include"), os.path.join(ROOT, "include", "attention_hpc"), CSRC]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unknown-pragmas",
+]
+
+
+def _sources() -> list[str]:
+    out = []
+    for dirpath, _, files in os.walk(CSRC):
+        for f in sorted(files):
+            if f.endswith((".cu", ".cpp")):
+                out.append(os.path.join(dirpath, f))
+    return sorted(out)
+
+
+def _headers() -> list[str]:
+    out = []
+    for base in (CSRC, os.path.join(ROOT, "include")):
+        for dirpath, _, files in os.walk(base):
+            out += [os.path.join(dirpath, f) for f in files if f.endswith((".h", ".hpp", ".cuh"))]
+    return out
+
+
+def _stamp(paths: list[str], extra: str = "") -> str:
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        h.update(p.encode())
+        with open(p, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
+def _compile(src: str, obj: str, verbose: bool) -> str:
+    cmd = ["nvcc", *NVCC_FLAGS, *[f"-I{i}" for i in INCLUDES], "-c", src, "-o", obj]
+    if src.endswith(".cpp"):
+        cmd[1:1] = ["-x", "cu"]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+    return r.stderr
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Builds the shared library if any source or header changed; returns its path."""
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    srcs = _sources()
+    stamp = _stamp(srcs + _headers(), " ".join(NVCC_FLAGS))
+    stamp_file = os.path.join(LIB_DIR, "build.stamp")
+    if not force and os.path.exists(LIB_PATH) and os.path.exists(stamp_file) and open(stamp_file).read() == stamp:
+        _build_cpp_tests(force)
+        return LIB_PATH
+    objs = [os.path.join(OBJ_DIR, os.path.relpath(s, CSRC).replace(os.sep, "_") + ".o") for s in srcs]
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+        logs = list(ex.map(lambda so: _compile(so[0], so[1], verbose), zip(srcs, objs)))
+    if verbose:
+        for s, log in zip(srcs, logs):
+            print(f"== {os.path.relpath(s, ROOT)}\n{log}")
+    link = ["nvcc", "-shared", "-o", LIB_PATH, *objs, "-cudart", "static"]
+    r = subprocess.run(link, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    with open(stamp_file, "w") as fh:
+        fh.write(stamp)
+    _build_cpp_tests(True)
+    return LIB_PATH
+
+
+def cpp_test_binary() -> str:
+    return os.path.join(ROOT, "tests", "cpp", "test_surface")
+
+
+def _build_cpp_tests(force: bool) -> None:
+    """The C++ surface test links the product library and (as its checker) the C oracle."""
+    src = os.path.join(ROOT, "tests", "cpp", "test_surface.cpp")
+    if not os.path.exists(src):
+        return
+    out = cpp_test_binary()
+    oracle_c = os.path.join(ROOT, "oracle", "oracle.c")
+    deps = [src, LIB_PATH, oracle_c]
+    if not force and os.path.exists(out) and all(os.path.getmtime(d) <= os.path.getmtime(out) for d in deps):
+        return
+    oracle_o = os.path.join(ROOT, "tests", "cpp", "oracle.o")
+    subprocess.run(["gcc", "-O2", "-std=c11", "-fopenmp", "-c", oracle_c, "-o", oracle_o], check=True)
+    cmd = ["g++", "-O2", "-std=c++17", "-Wall", *[f"-I{i}" for i in INCLUDES[:2]], src, oracle_o, "-o", out,
+           f"-L{LIB_DIR}", "-lahpc_b200", f"-Wl,-rpath,$ORIGIN/../../attention_b200/lib", "-fopenmp", "-lm"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building the C++ surface test failed:\n{r.stdout}\n{r.stderr}")
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(path)

@@ -1,0 +1,190 @@
+// Library-level entry points of the C ABI: version, error text, device discovery, staging
+// arenas and the multi-GPU partition arithmetic.
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <utility>
+
+#include "common.cuh"
+
+namespace ahpc {
+
+std::string& last_error() {
+    static thread_local std::string text;
+    return text;
+}
+
+ahpc_status fail(ahpc_status code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    last_error() = buf;
+    return code;
+}
+
+namespace {
+struct DeviceTable {
+    std::mutex mu;
+    bool probed = false;
+    int count = 0;
+    std::map<int, cudaDeviceProp> props;
+    std::map<std::pair<int, int>, std::pair<void*, size_t>> arenas;
+};
+DeviceTable& table() {
+    static DeviceTable t;
+    return t;
+}
+
+// Number of devices, and the properties of each, read once.
+int probe_locked(DeviceTable& t) {
+    if (t.probed) return t.count;
+    t.probed = true;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        n = 0;
+    }
+    for (int d = 0; d < n; ++d) {
+        cudaDeviceProp p;
+        if (cudaGetDeviceProperties(&p, d) == cudaSuccess) t.props[d] = p;
+    }
+    t.count = n;
+    return n;
+}
+}  // namespace
+
+ahpc_status use_device(int device) {
+    DeviceTable& t = table();
+    {
+        std::lock_guard<std::mutex> lock(t.mu);
+        int n = probe_locked(t);
+        if (n == 0) return fail(AHPC_BACKEND_NOT_AVAILABLE, "no CUDA device is visible; this library has no CPU path");
+        auto it = t.props.find(device);
+        if (device < 0 || it == t.props.end())
+            return fail(AHPC_INVALID_PARAMETERS, "device %d does not exist (%d visible)", device, n);
+        if (it->second.major != 10)
+            return fail(AHPC_BACKEND_NOT_AVAILABLE,
+                        "device %d is sm_%d%d; the kernels in this library are built for sm_100a only",
+                        device, it->second.major, it->second.minor);
+    }
+    AHPC_CUDA_OK(cudaSetDevice(device));
+    return AHPC_SUCCESS;
+}
+
+int sm_count(int device) {
+    DeviceTable& t = table();
+    std::lock_guard<std::mutex> lock(t.mu);
+    probe_locked(t);
+    auto it = t.props.find(device);
+    return it == t.props.end() ? 0 : it->second.multiProcessorCount;
+}
+
+bool is_host_pointer(const void* p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return true;
+    }
+    return attr.type == cudaMemoryTypeUnregistered || attr.type == cudaMemoryTypeHost;
+}
+
+ahpc_status staging_buffer(int device, int slot, size_t bytes, void** out) {
+    DeviceTable& t = table();
+    std::lock_guard<std::mutex> lock(t.mu);
+    auto& arena = t.arenas[{device, slot}];
+    if (arena.second < bytes) {
+        if (arena.first) {
+            AHPC_CUDA_OK(cudaDeviceSynchronize());
+            AHPC_CUDA_OK(cudaFree(arena.first));
+            arena = {nullptr, 0};
+        }
+        size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+        void* p = nullptr;
+        AHPC_CUDA_OK(cudaMalloc(&p, want));
+        arena = {p, want};
+    }
+    *out = arena.first;
+    return AHPC_SUCCESS;
+}
+
+}  // namespace ahpc
+
+using namespace ahpc;
+
+extern "C" {
+
+const char* ahpc_version(void) { return "0.1.0"; }
+
+const char* ahpc_last_error_string(void) { return last_error().c_str(); }
+
+int32_t ahpc_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    int usable = 0;
+    for (int d = 0; d < n; ++d) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d) == cudaSuccess && major == 10) ++usable;
+    }
+    return usable;
+}
+
+ahpc_status ahpc_get_device_info(int32_t device, ahpc_device_info* out) {
+    if (!out) return fail(AHPC_INVALID_INPUT, "ahpc_get_device_info: out is NULL");
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        (void)cudaGetLastError();
+        return fail(AHPC_BACKEND_NOT_AVAILABLE, "no CUDA device is visible");
+    }
+    if (device < 0 || device >= n) return fail(AHPC_INVALID_PARAMETERS, "device %d does not exist (%d visible)", device, n);
+    cudaDeviceProp p;
+    AHPC_CUDA_OK(cudaGetDeviceProperties(&p, device));
+    memset(out, 0, sizeof(*out));
+    strncpy(out->name, p.name, sizeof(out->name) - 1);
+    out->total_memory_bytes = p.totalGlobalMem;
+    out->cc_major = p.major;
+    out->cc_minor = p.minor;
+    out->sm_count = p.multiProcessorCount;
+    out->max_threads_per_block = p.maxThreadsPerBlock;
+    out->max_shared_memory_per_block = p.sharedMemPerBlockOptin;
+    int v = 0;
+    if (cudaDriverGetVersion(&v) == cudaSuccess) out->driver_version = v;
+    if (cudaRuntimeGetVersion(&v) == cudaSuccess) out->runtime_version = v;
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_fa_strides(int32_t layout, int64_t batch, int64_t heads, int64_t seq, int64_t head_dim,
+                            int64_t strides[4]) {
+    if (!strides) return fail(AHPC_INVALID_INPUT, "ahpc_fa_strides: strides is NULL");
+    (void)batch;
+    if (layout == AHPC_LAYOUT_BHSD) {
+        strides[0] = heads * seq * head_dim;
+        strides[1] = seq * head_dim;
+        strides[2] = head_dim;
+        strides[3] = 1;
+    } else if (layout == AHPC_LAYOUT_BSHD) {
+        strides[0] = seq * heads * head_dim;
+        strides[1] = head_dim;
+        strides[2] = heads * head_dim;
+        strides[3] = 1;
+    } else {
+        return fail(AHPC_INVALID_PARAMETERS, "unknown layout %d", layout);
+    }
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_shard_range(int64_t units, int32_t world, int32_t rank, int64_t* begin_out, int64_t* end_out) {
+    if (units < 0 || world <= 0 || rank < 0 || rank >= world || !begin_out || !end_out)
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_shard_range: units=%lld world=%d rank=%d", (long long)units, world, rank);
+    int64_t base = units / world, extra = units % world;
+    int64_t begin = rank * base + (rank < extra ? rank : extra);
+    *begin_out = begin;
+    *end_out = begin + base + (rank < extra ? 1 : 0);
+    return AHPC_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,82 @@
+// Shared host/device helpers for the library's translation units.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "ahpc.h"
+
+namespace ahpc {
+
+// ---- per-thread error text ---------------------------------------------------------------
+std::string& last_error();                       // defined in abi_core.cu
+ahpc_status fail(ahpc_status code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+
+#define AHPC_CUDA_OK(expr)                                                                      \
+    do {                                                                                        \
+        cudaError_t e__ = (expr);                                                               \
+        if (e__ != cudaSuccess)                                                                 \
+            return ::ahpc::fail(e__ == cudaErrorMemoryAllocation ? AHPC_MEMORY_ALLOCATION_FAILED \
+                                                                 : AHPC_COMPUTATION_FAILED,     \
+                                "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__),        \
+                                __FILE__, __LINE__);                                            \
+    } while (0)
+
+#define AHPC_TRY(expr)                         \
+    do {                                       \
+        ahpc_status s__ = (expr);              \
+        if (s__ != AHPC_SUCCESS) return s__;   \
+    } while (0)
+
+// ---- devices --------------------------------------------------------------------------------
+// Checks that `device` exists and is an sm_100-family part; makes it current.
+ahpc_status use_device(int device);
+int sm_count(int device);
+
+// True when p points to memory the GPU cannot address directly (pageable or unknown host memory
+// is reported as "host"; pinned/managed/device memory as device-accessible).
+bool is_host_pointer(const void* p);
+
+// Grow-only device scratch owned by the library, one arena per (device, slot).  Used for staging
+// host tensors.  The returned pointer stays valid until the next request for the same slot that
+// needs more room.
+ahpc_status staging_buffer(int device, int slot, size_t bytes, void** out);
+
+inline size_t dtype_size(int dtype) { return dtype == AHPC_F32 ? 4 : 2; }
+inline bool dtype_valid(int dtype) { return dtype == AHPC_F32 || dtype == AHPC_F16 || dtype == AHPC_BF16; }
+
+// ---- element conversion on the device ------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);   // round to nearest even
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// ---- kernel launchers implemented in other translation units ------------------------------
+struct FaLaunch {                 // validated, device-pointer form of ahpc_fa_args
+    const void *q, *k, *v;
+    void* out;
+    const float* mask;
+    float* lse;
+    int dtype, batch, heads, seq_q, seq_kv, head_dim;
+    int64_t qs[4], ks[4], vs[4], os[4];
+    float scale;
+    int causal;
+    int device;
+    cudaStream_t stream;
+};
+ahpc_status launch_fa_simt(const FaLaunch& a);     // fa_simt.cu
+ahpc_status launch_fa_tc(const FaLaunch& a);       // fa_tc.cu
+bool fa_tc_supported(const FaLaunch& a, const char** why);
+
+}  // namespace ahpc

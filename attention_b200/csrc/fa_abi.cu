@@ -1,0 +1,127 @@
+// ahpc_fa_fwd: argument validation, host-pointer staging and kernel selection for the
+// FlashAttention forward.
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+
+using namespace ahpc;
+
+namespace {
+
+// Number of elements spanned by a [B,H,S,D] view with the given element strides.
+int64_t span_elems(const int64_t st[4], int64_t B, int64_t H, int64_t S, int64_t D) {
+    return (B - 1) * st[0] + (H - 1) * st[1] + (S - 1) * st[2] + (D - 1) * st[3] + 1;
+}
+
+ahpc_status validate(const ahpc_fa_args* a) {
+    if (!a) return fail(AHPC_INVALID_INPUT, "ahpc_fa_fwd: args is NULL");
+    if (!a->q || !a->k || !a->v || !a->out) return fail(AHPC_INVALID_INPUT, "ahpc_fa_fwd: q, k, v and out must not be NULL");
+    if (!dtype_valid(a->dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: unknown dtype %d", a->dtype);
+    if (a->batch <= 0 || a->heads <= 0 || a->seq_q <= 0 || a->seq_kv <= 0 || a->head_dim <= 0)
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: dimensions must be positive (B=%d H=%d Sq=%d Skv=%d D=%d)",
+                    a->batch, a->heads, a->seq_q, a->seq_kv, a->head_dim);
+    const int64_t* sts[4] = {a->q_strides, a->k_strides, a->v_strides, a->o_strides};
+    for (int t = 0; t < 4; ++t)
+        for (int i = 0; i < 4; ++i)
+            if (sts[t][i] < 0) return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: negative stride");
+    if (a->kernel < AHPC_FA_KERNEL_AUTO || a->kernel > AHPC_FA_KERNEL_TC)
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: unknown kernel selector %d", a->kernel);
+    if (!std::isfinite(a->scale)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: scale is not finite");
+    return AHPC_SUCCESS;
+}
+
+void to_launch(const ahpc_fa_args* a, FaLaunch& l) {
+    l.q = a->q; l.k = a->k; l.v = a->v; l.out = a->out; l.mask = a->mask; l.lse = a->lse;
+    l.dtype = a->dtype; l.batch = a->batch; l.heads = a->heads; l.seq_q = a->seq_q; l.seq_kv = a->seq_kv;
+    l.head_dim = a->head_dim;
+    for (int i = 0; i < 4; ++i) {
+        l.qs[i] = a->q_strides[i]; l.ks[i] = a->k_strides[i]; l.vs[i] = a->v_strides[i]; l.os[i] = a->o_strides[i];
+    }
+    l.scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)a->head_dim);
+    l.causal = a->causal != 0;
+    l.device = a->device;
+    l.stream = static_cast<cudaStream_t>(a->stream);
+}
+
+int pick_kernel(const FaLaunch& l, int requested, const char** why) {
+    const char* reason = nullptr;
+    bool tc_ok = fa_tc_supported(l, &reason);
+    if (why) *why = reason;
+    if (requested == AHPC_FA_KERNEL_SIMT) return AHPC_FA_KERNEL_SIMT;
+    if (requested == AHPC_FA_KERNEL_TC) return tc_ok ? AHPC_FA_KERNEL_TC : -1;
+    return tc_ok ? AHPC_FA_KERNEL_TC : AHPC_FA_KERNEL_SIMT;
+}
+
+ahpc_status run(const FaLaunch& l, int requested) {
+    const char* why = nullptr;
+    int kernel = pick_kernel(l, requested, &why);
+    if (kernel < 0) return fail(AHPC_UNSUPPORTED_OPERATION, "tensor-core kernel not applicable: %s", why ? why : "?");
+    return kernel == AHPC_FA_KERNEL_TC ? launch_fa_tc(l) : launch_fa_simt(l);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t ahpc_fa_select_kernel(const ahpc_fa_args* args) {
+    if (validate(args) != AHPC_SUCCESS) return -1;
+    FaLaunch l;
+    to_launch(args, l);
+    return pick_kernel(l, args->kernel, nullptr);
+}
+
+size_t ahpc_fa_workspace_bytes(int32_t dtype, int64_t batch, int64_t heads, int64_t seq_q, int64_t seq_kv,
+                               int64_t head_dim, int32_t with_mask) {
+    if (!dtype_valid(dtype) || batch <= 0 || heads <= 0 || seq_q <= 0 || seq_kv <= 0 || head_dim <= 0) return 0;
+    size_t es = dtype_size(dtype);
+    size_t qo = (size_t)batch * heads * seq_q * head_dim * es;
+    size_t kv = (size_t)batch * heads * seq_kv * head_dim * es;
+    size_t m = with_mask ? (size_t)batch * seq_q * seq_kv * sizeof(float) : 0;
+    return 2 * qo + 2 * kv + m;
+}
+
+ahpc_status ahpc_fa_fwd(const ahpc_fa_args* args) {
+    AHPC_TRY(validate(args));
+    AHPC_TRY(use_device(args->device));
+    FaLaunch l;
+    to_launch(args, l);
+
+    const bool host_q = is_host_pointer(args->q), host_k = is_host_pointer(args->k);
+    const bool host_v = is_host_pointer(args->v), host_o = is_host_pointer(args->out);
+    const bool host_m = args->mask && is_host_pointer(args->mask);
+    if (!(host_q || host_k || host_v || host_o || host_m)) return run(l, args->kernel);
+
+    // Host tensors: stage each one into a library-owned device arena, run on the caller's stream,
+    // copy the result back and wait.  Spans are copied as they lie, so strided views keep working.
+    if (args->lse && is_host_pointer(args->lse))
+        return fail(AHPC_INVALID_INPUT, "ahpc_fa_fwd: lse must be a device pointer");
+    const size_t es = dtype_size(l.dtype);
+    const int64_t nq = span_elems(l.qs, l.batch, l.heads, l.seq_q, l.head_dim);
+    const int64_t nk = span_elems(l.ks, l.batch, l.heads, l.seq_kv, l.head_dim);
+    const int64_t nv = span_elems(l.vs, l.batch, l.heads, l.seq_kv, l.head_dim);
+    const int64_t no = span_elems(l.os, l.batch, l.heads, l.seq_q, l.head_dim);
+    void *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr, *dm = nullptr;
+    if (host_q) { AHPC_TRY(staging_buffer(l.device, 0, nq * es, &dq)); AHPC_CUDA_OK(cudaMemcpyAsync(dq, args->q, nq * es, cudaMemcpyHostToDevice, l.stream)); l.q = dq; }
+    if (host_k) { AHPC_TRY(staging_buffer(l.device, 1, nk * es, &dk)); AHPC_CUDA_OK(cudaMemcpyAsync(dk, args->k, nk * es, cudaMemcpyHostToDevice, l.stream)); l.k = dk; }
+    if (host_v) { AHPC_TRY(staging_buffer(l.device, 2, nv * es, &dv)); AHPC_CUDA_OK(cudaMemcpyAsync(dv, args->v, nv * es, cudaMemcpyHostToDevice, l.stream)); l.v = dv; }
+    if (host_o) { AHPC_TRY(staging_buffer(l.device, 3, no * es, &dout)); l.out = dout; }
+    if (host_m) {
+        size_t mb = (size_t)l.batch * l.seq_q * l.seq_kv * sizeof(float);
+        AHPC_TRY(staging_buffer(l.device, 4, mb, &dm));
+        AHPC_CUDA_OK(cudaMemcpyAsync(dm, args->mask, mb, cudaMemcpyHostToDevice, l.stream));
+        l.mask = static_cast<const float*>(dm);
+    }
+    if (host_o) {
+        // Elements of the span the kernel does not write (strided views) must survive the round trip.
+        bool dense = no == (int64_t)l.batch * l.heads * l.seq_q * l.head_dim;
+        if (!dense) AHPC_CUDA_OK(cudaMemcpyAsync(dout, args->out, no * es, cudaMemcpyHostToDevice, l.stream));
+    }
+    AHPC_TRY(run(l, args->kernel));
+    if (host_o) AHPC_CUDA_OK(cudaMemcpyAsync(args->out, dout, no * es, cudaMemcpyDeviceToHost, l.stream));
+    AHPC_CUDA_OK(cudaStreamSynchronize(l.stream));
+    return AHPC_SUCCESS;
+}
+
+}  // extern "C"

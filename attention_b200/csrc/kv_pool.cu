@@ -1,0 +1,653 @@
+// Device-resident page allocator and KV scatter/gather for the paged KV pool.
+//
+// Replaces, on the device, PagePool (FIFO std::queue of pages: pop front / push back,
+// src/algorithms/paged_attention.cpp:16-39), the per-sequence page lists of SequenceState
+// (src/algorithms/paged_attention.hpp:87-122) and append_kv_cache / get_kv_cache
+// (paged_attention.cpp:434-490; GPU analogue update_kv_cache_kernel, cuda_kernels.cu:518-563).
+//
+// All allocator kernels run as ONE thread block so that their effect is a deterministic function
+// of the call sequence: pages are handed out in ring order to the sequences of a call in the
+// order the call lists them, and freed pages re-enter the ring in the order the reference's
+// loops would push them.  That makes the block table bit-identical to a sequential CPU model.
+#include <cub/block/block_scan.cuh>
+
+#include <algorithm>
+#include <cstring>
+
+#include "pool.cuh"
+
+namespace ahpc {
+namespace {
+
+constexpr int ALLOC_THREADS = 256;
+using BlockScan = cub::BlockScan<int, ALLOC_THREADS>;
+
+__global__ void pool_init_kernel(int32_t* table, int64_t table_n, int32_t* seq_len, int32_t* seq_pages, int max_seqs,
+                                 int32_t* refcount, int32_t* ring, int num_pages, int has_order, long long* ctrl) {
+    const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, nth = gridDim.x * (int64_t)blockDim.x;
+    for (int64_t i = tid; i < table_n; i += nth) table[i] = -1;
+    for (int64_t i = tid; i < max_seqs; i += nth) { seq_len[i] = 0; seq_pages[i] = 0; }
+    for (int64_t i = tid; i < num_pages; i += nth) {
+        refcount[i] = 0;
+        if (!has_order) ring[i] = (int32_t)i;
+    }
+    if (tid == 0) { ctrl[CTRL_HEAD] = 0; ctrl[CTRL_COUNT] = num_pages; ctrl[CTRL_ERROR] = 0; ctrl[3] = 0; }
+}
+
+// args layout: seqs[n] | n_tokens[n] | tok_offset[n] | page_offset[n] (written here)
+__global__ void __launch_bounds__(ALLOC_THREADS)
+pool_append_alloc_kernel(int32_t* args, int n, int32_t* table, int32_t* seq_len, int32_t* seq_pages, int32_t* refcount,
+                         const int32_t* ring, long long* ctrl, int num_pages, int page_size, int max_pages) {
+    __shared__ typename BlockScan::TempStorage scan_tmp;
+    __shared__ int s_total;
+    const int32_t* seqs = args;
+    const int32_t* ntok = args + n;
+    int32_t* page_off = args + 3 * (size_t)n;
+    const int tid = threadIdx.x;
+
+    // pages each sequence still needs, and their exclusive prefix over the call order
+    int running = 0;
+    for (int base = 0; base < n; base += ALLOC_THREADS) {
+        const int i = base + tid;
+        int need = 0;
+        if (i < n) {
+            const int s = seqs[i];
+            need = (seq_len[s] + ntok[i] + page_size - 1) / page_size - seq_pages[s];
+            if (need < 0) need = 0;
+        }
+        int excl, total;
+        BlockScan(scan_tmp).ExclusiveSum(need, excl, total);
+        if (i < n) page_off[i] = running + excl;
+        running += total;
+        __syncthreads();
+    }
+    if (tid == 0) s_total = running;
+    __syncthreads();
+    const int total = s_total;
+    const long long head = ctrl[CTRL_HEAD], count = ctrl[CTRL_COUNT];
+    if (total > count) {                      // the host admits calls against a lower bound; never expected
+        if (tid == 0) ctrl[CTRL_ERROR] = 1;
+        return;
+    }
+    // hand out ring[head + f] for the flattened (sequence, new page) index f
+    for (int f = tid; f < total; f += ALLOC_THREADS) {
+        int lo = 0, hi = n - 1;               // last i with page_off[i] <= f
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (page_off[mid] <= f) lo = mid; else hi = mid - 1;
+        }
+        const int s = seqs[lo];
+        const int col = seq_pages[s] + (f - page_off[lo]);
+        const int32_t page = ring[(head + f) % num_pages];
+        if (col >= max_pages || page < 0 || page >= num_pages) { ctrl[CTRL_ERROR] = 2; continue; }
+        table[(size_t)s * max_pages + col] = page;
+        refcount[page] = 1;
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += ALLOC_THREADS) {
+        const int s = seqs[i];
+        const int new_len = seq_len[s] + ntok[i];
+        seq_len[s] = new_len;
+        seq_pages[s] = max(seq_pages[s], (new_len + page_size - 1) / page_size);
+    }
+    if (tid == 0) { ctrl[CTRL_HEAD] = (head + total) % num_pages; ctrl[CTRL_COUNT] = count - total; }
+}
+
+// One thread per 16-byte piece of the pool.  src: [tokens][heads][head_dim] of TIn.
+template <typename TIn, typename TPool>
+__global__ void pool_scatter_kernel(const TIn* __restrict__ k_src, const TIn* __restrict__ v_src, TPool* __restrict__ k_data,
+                                    TPool* __restrict__ v_data, const int32_t* __restrict__ args, int n,
+                                    const int32_t* __restrict__ table, const int32_t* __restrict__ seq_len, int heads,
+                                    int head_dim, int page_size, int max_pages, size_t page_elems) {
+    constexpr int VEC = 16 / sizeof(TPool);
+    const int i = blockIdx.y;
+    const int s = args[i], nt = args[n + i], tok0 = args[2 * (size_t)n + i];
+    const int pieces = head_dim / VEC;
+    const int64_t work = (int64_t)nt * heads * pieces;
+    const int first_pos = seq_len[s] - nt;          // seq_len already includes this call's tokens
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < work; w += (int64_t)gridDim.x * blockDim.x) {
+        const int piece = (int)(w % pieces);
+        const int head = (int)((w / pieces) % heads);
+        const int t = (int)(w / ((int64_t)pieces * heads));
+        const int pos = first_pos + t;
+        const int page = table[(size_t)s * max_pages + pos / page_size];
+        if (page < 0) continue;
+        const int slot = pos % page_size;
+        const size_t src = ((size_t)(tok0 + t) * heads + head) * head_dim + (size_t)piece * VEC;
+        TPool kv[VEC], vv[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            kv[e] = from_f32<TPool>(to_f32<TIn>(k_src[src + e]));
+            vv[e] = from_f32<TPool>(to_f32<TIn>(v_src[src + e]));
+        }
+        const size_t kd = k_piece_offset(page_elems, heads, page_size, head_dim, VEC, page, head, slot, piece);
+        const size_t vd = v_row_offset(page_elems, page_size, head_dim, page, head, slot) + (size_t)piece * VEC;
+        *reinterpret_cast<uint4*>(k_data + kd) = *reinterpret_cast<const uint4*>(kv);
+        *reinterpret_cast<uint4*>(v_data + vd) = *reinterpret_cast<const uint4*>(vv);
+    }
+}
+
+// dst: [n][heads][head_dim] of TOut, tokens [start, start+n) of sequence s.
+template <typename TOut, typename TPool>
+__global__ void pool_gather_kernel(TOut* __restrict__ k_dst, TOut* __restrict__ v_dst, const TPool* __restrict__ k_data,
+                                   const TPool* __restrict__ v_data, int s, int start, int n,
+                                   const int32_t* __restrict__ table, int heads, int head_dim, int page_size,
+                                   int max_pages, size_t page_elems) {
+    constexpr int VEC = 16 / sizeof(TPool);
+    const int pieces = head_dim / VEC;
+    const int64_t work = (int64_t)n * heads * pieces;
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < work; w += (int64_t)gridDim.x * blockDim.x) {
+        const int piece = (int)(w % pieces);
+        const int head = (int)((w / pieces) % heads);
+        const int t = (int)(w / ((int64_t)pieces * heads));
+        const int pos = start + t;
+        const int page = table[(size_t)s * max_pages + pos / page_size];
+        const size_t dst = ((size_t)t * heads + head) * head_dim + (size_t)piece * VEC;
+        if (page < 0) {
+            for (int e = 0; e < VEC; ++e) { k_dst[dst + e] = from_f32<TOut>(0.f); v_dst[dst + e] = from_f32<TOut>(0.f); }
+            continue;
+        }
+        const int slot = pos % page_size;
+        const size_t kd = k_piece_offset(page_elems, heads, page_size, head_dim, VEC, page, head, slot, piece);
+        const size_t vd = v_row_offset(page_elems, page_size, head_dim, page, head, slot) + (size_t)piece * VEC;
+        TPool kv[VEC], vv[VEC];
+        *reinterpret_cast<uint4*>(kv) = *reinterpret_cast<const uint4*>(k_data + kd);
+        *reinterpret_cast<uint4*>(vv) = *reinterpret_cast<const uint4*>(v_data + vd);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            k_dst[dst + e] = from_f32<TOut>(to_f32<TPool>(kv[e]));
+            v_dst[dst + e] = from_f32<TOut>(to_f32<TPool>(vv[e]));
+        }
+    }
+}
+
+// Drops the pages [keep, seq_pages) of sequence s.  `reverse` = release from the back (truncate,
+// paged_attention.cpp:409-413), otherwise front to back (reset/destroy, :360-362).  Pages whose
+// reference count reaches zero re-enter the ring in that order.
+__global__ void __launch_bounds__(ALLOC_THREADS)
+pool_release_kernel(int s, int keep, int new_len, int reverse, int32_t* table, int32_t* seq_len, int32_t* seq_pages,
+                    int32_t* refcount, int32_t* ring, long long* ctrl, int num_pages, int max_pages) {
+    __shared__ typename BlockScan::TempStorage scan_tmp;
+    const int tid = threadIdx.x;
+    const int have = seq_pages[s];
+    const int cnt = have - keep;
+    const long long head = ctrl[CTRL_HEAD], count = ctrl[CTRL_COUNT];
+    int running = 0;
+    for (int base = 0; base < cnt; base += ALLOC_THREADS) {
+        const int j = base + tid;
+        int freed = 0;
+        int32_t page = -1;
+        if (j < cnt) {
+            const int col = reverse ? have - 1 - j : keep + j;
+            page = table[(size_t)s * max_pages + col];
+            table[(size_t)s * max_pages + col] = -1;
+            if (page >= 0 && page < num_pages) freed = atomicSub(&refcount[page], 1) == 1;
+            else ctrl[CTRL_ERROR] = 3;
+        }
+        int excl, total;
+        BlockScan(scan_tmp).ExclusiveSum(freed, excl, total);
+        if (freed) ring[(head + count + running + excl) % num_pages] = page;
+        running += total;
+        __syncthreads();
+    }
+    if (tid == 0) {
+        ctrl[CTRL_COUNT] = count + running;
+        if (cnt > 0) seq_pages[s] = keep;
+        seq_len[s] = new_len;
+    }
+}
+
+// dst shares the first `full` pages of src; if `rem` tokens of a partly used page follow, dst gets
+// a fresh page for them (filled by pool_copy_partial_kernel).
+__global__ void __launch_bounds__(ALLOC_THREADS)
+pool_fork_kernel(int src, int dst, int full, int rem, int page_size, int32_t* table, int32_t* seq_len, int32_t* seq_pages,
+                 int32_t* refcount, const int32_t* ring, long long* ctrl, int num_pages, int max_pages) {
+    const int tid = threadIdx.x;
+    for (int j = tid; j < full; j += ALLOC_THREADS) {
+        const int32_t page = table[(size_t)src * max_pages + j];
+        table[(size_t)dst * max_pages + j] = page;
+        if (page >= 0 && page < num_pages) atomicAdd(&refcount[page], 1);
+        else ctrl[CTRL_ERROR] = 4;
+    }
+    if (tid == 0) {
+        if (rem) {
+            const long long head = ctrl[CTRL_HEAD], count = ctrl[CTRL_COUNT];
+            if (count < 1) ctrl[CTRL_ERROR] = 1;
+            else {
+                const int32_t page = ring[head % num_pages];
+                table[(size_t)dst * max_pages + full] = page;
+                refcount[page] = 1;
+                ctrl[CTRL_HEAD] = (head + 1) % num_pages;
+                ctrl[CTRL_COUNT] = count - 1;
+            }
+        }
+        seq_pages[dst] = full + (rem ? 1 : 0);
+        seq_len[dst] = full * page_size + rem;
+    }
+}
+
+template <typename TPool>
+__global__ void pool_copy_partial_kernel(TPool* __restrict__ k_data, TPool* __restrict__ v_data, const int32_t* __restrict__ table,
+                                         int src, int dst, int col, int rem, int heads, int head_dim, int page_size,
+                                         int max_pages, size_t page_elems) {
+    constexpr int VEC = 16 / sizeof(TPool);
+    const int from = table[(size_t)src * max_pages + col], to = table[(size_t)dst * max_pages + col];
+    if (from < 0 || to < 0) return;
+    const int pieces = head_dim / VEC;
+    const int64_t work = (int64_t)rem * heads * pieces;
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < work; w += (int64_t)gridDim.x * blockDim.x) {
+        const int piece = (int)(w % pieces);
+        const int head = (int)((w / pieces) % heads);
+        const int slot = (int)(w / ((int64_t)pieces * heads));
+        const size_t ks = k_piece_offset(page_elems, heads, page_size, head_dim, VEC, from, head, slot, piece);
+        const size_t kd = k_piece_offset(page_elems, heads, page_size, head_dim, VEC, to, head, slot, piece);
+        const size_t vs = v_row_offset(page_elems, page_size, head_dim, from, head, slot) + (size_t)piece * VEC;
+        const size_t vd = v_row_offset(page_elems, page_size, head_dim, to, head, slot) + (size_t)piece * VEC;
+        *reinterpret_cast<uint4*>(k_data + kd) = *reinterpret_cast<const uint4*>(k_data + ks);
+        *reinterpret_cast<uint4*>(v_data + vd) = *reinterpret_cast<const uint4*>(v_data + vs);
+    }
+}
+
+template <typename TIn, typename TPool>
+void scatter_launch(ahpc_pool* p, const void* k, const void* v, int n, int max_tokens, cudaStream_t st) {
+    const int pieces = p->cfg.head_dim / (16 / (int)sizeof(TPool));
+    int64_t work = (int64_t)max_tokens * p->cfg.heads * pieces;
+    int bx = (int)std::min<int64_t>((work + 255) / 256, 4096);
+    dim3 grid(std::max(bx, 1), n);
+    pool_scatter_kernel<TIn, TPool><<<grid, 256, 0, st>>>(
+        static_cast<const TIn*>(k), static_cast<const TIn*>(v), static_cast<TPool*>(p->k_data), static_cast<TPool*>(p->v_data),
+        p->call_args, n, p->table, p->seq_len, p->cfg.heads, p->cfg.head_dim, p->cfg.page_size, p->cfg.max_pages_per_seq,
+        p->page_elems);
+}
+
+template <typename TPool>
+ahpc_status scatter_dispatch(ahpc_pool* p, const void* k, const void* v, int kv_dtype, int n, int max_tokens, cudaStream_t st) {
+    switch (kv_dtype) {
+        case AHPC_F32: scatter_launch<float, TPool>(p, k, v, n, max_tokens, st); break;
+        case AHPC_F16: scatter_launch<__half, TPool>(p, k, v, n, max_tokens, st); break;
+        case AHPC_BF16: scatter_launch<__nv_bfloat16, TPool>(p, k, v, n, max_tokens, st); break;
+        default: return fail(AHPC_INVALID_PARAMETERS, "unknown kv dtype %d", kv_dtype);
+    }
+    AHPC_CUDA_OK(cudaGetLastError());
+    return AHPC_SUCCESS;
+}
+
+template <typename TOut, typename TPool>
+void gather_launch(ahpc_pool* p, void* k, void* v, int seq, int start, int n, cudaStream_t st) {
+    const int pieces = p->cfg.head_dim / (16 / (int)sizeof(TPool));
+    int64_t work = (int64_t)n * p->cfg.heads * pieces;
+    int bx = (int)std::min<int64_t>((work + 255) / 256, 8192);
+    pool_gather_kernel<TOut, TPool><<<std::max(bx, 1), 256, 0, st>>>(
+        static_cast<TOut*>(k), static_cast<TOut*>(v), static_cast<const TPool*>(p->k_data), static_cast<const TPool*>(p->v_data),
+        seq, start, n, p->table, p->cfg.heads, p->cfg.head_dim, p->cfg.page_size, p->cfg.max_pages_per_seq, p->page_elems);
+}
+
+template <typename TPool>
+ahpc_status gather_dispatch(ahpc_pool* p, void* k, void* v, int out_dtype, int seq, int start, int n, cudaStream_t st) {
+    switch (out_dtype) {
+        case AHPC_F32: gather_launch<float, TPool>(p, k, v, seq, start, n, st); break;
+        case AHPC_F16: gather_launch<__half, TPool>(p, k, v, seq, start, n, st); break;
+        case AHPC_BF16: gather_launch<__nv_bfloat16, TPool>(p, k, v, seq, start, n, st); break;
+        default: return fail(AHPC_INVALID_PARAMETERS, "unknown output dtype %d", out_dtype);
+    }
+    AHPC_CUDA_OK(cudaGetLastError());
+    return AHPC_SUCCESS;
+}
+
+ahpc_status check_seq(const ahpc_pool* p, int seq, const char* who) {
+    if (seq < 0 || seq >= p->cfg.max_seqs || !p->h_live[seq]) return fail(AHPC_INVALID_INPUT, "%s: sequence %d not found", who, seq);
+    return AHPC_SUCCESS;
+}
+
+// Exact number of free pages, read from the device (synchronises the stream).
+ahpc_status refresh_free_count(ahpc_pool* p, cudaStream_t st) {
+    long long c[4];
+    AHPC_CUDA_OK(cudaMemcpyAsync(c, p->ctrl, sizeof(c), cudaMemcpyDeviceToHost, st));
+    AHPC_CUDA_OK(cudaStreamSynchronize(st));
+    p->free_lower_bound = c[CTRL_COUNT];
+    return AHPC_SUCCESS;
+}
+
+}  // namespace
+}  // namespace ahpc
+
+using namespace ahpc;
+
+extern "C" {
+
+ahpc_status ahpc_pool_create(ahpc_pool** out, const ahpc_pool_config* c) {
+    if (!out || !c) return fail(AHPC_INVALID_INPUT, "ahpc_pool_create: NULL argument");
+    *out = nullptr;
+    if (!dtype_valid(c->dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_create: unknown dtype %d", c->dtype);
+    if (c->num_pages <= 0 || c->page_size <= 0 || c->heads <= 0 || c->head_dim <= 0 || c->max_seqs <= 0 || c->max_pages_per_seq <= 0)
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_create: all sizes must be positive");
+    const int vec = 16 / (int)dtype_size(c->dtype);
+    if (c->head_dim % vec) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_create: head_dim %d must be a multiple of %d", c->head_dim, vec);
+    if (c->free_order) {
+        std::vector<uint8_t> seen(c->num_pages, 0);
+        for (int i = 0; i < c->num_pages; ++i) {
+            int v = c->free_order[i];
+            if (v < 0 || v >= c->num_pages || seen[v]) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_create: free_order is not a permutation");
+            seen[v] = 1;
+        }
+    }
+    AHPC_TRY(use_device(c->device));
+    ahpc_pool* p = new ahpc_pool();
+    p->cfg = *c;
+    p->cfg.free_order = nullptr;
+    p->vec = vec;
+    p->elem_size = dtype_size(c->dtype);
+    p->page_elems = (size_t)c->heads * c->page_size * c->head_dim;
+    const size_t data_bytes = (size_t)c->num_pages * p->page_elems * p->elem_size;
+    const size_t table_n = (size_t)c->max_seqs * c->max_pages_per_seq;
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](void** ptr, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(ptr, bytes); };
+    alloc(&p->k_data, data_bytes);
+    alloc(&p->v_data, data_bytes);
+    alloc((void**)&p->table, table_n * sizeof(int32_t));
+    alloc((void**)&p->seq_len, c->max_seqs * sizeof(int32_t));
+    alloc((void**)&p->seq_pages, c->max_seqs * sizeof(int32_t));
+    alloc((void**)&p->refcount, c->num_pages * sizeof(int32_t));
+    alloc((void**)&p->ring, c->num_pages * sizeof(int32_t));
+    alloc((void**)&p->ctrl, 4 * sizeof(long long));
+    alloc((void**)&p->call_args, (4 * (size_t)c->max_seqs + 8) * sizeof(int32_t));
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        ahpc_pool_destroy(p);
+        return fail(AHPC_MEMORY_ALLOCATION_FAILED, "ahpc_pool_create: cudaMalloc failed (%s) for %d pages of %zu bytes",
+                    cudaGetErrorString(e), c->num_pages, 2 * p->page_elems * p->elem_size);
+    }
+    if (c->free_order) e = cudaMemcpy(p->ring, c->free_order, c->num_pages * sizeof(int32_t), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) {
+        pool_init_kernel<<<256, 256>>>(p->table, (int64_t)table_n, p->seq_len, p->seq_pages, c->max_seqs, p->refcount, p->ring,
+                                       c->num_pages, c->free_order != nullptr, p->ctrl);
+        e = cudaGetLastError();
+    }
+    // Pages start zeroed so that unused slots never hold NaN payloads.
+    if (e == cudaSuccess) e = cudaMemset(p->k_data, 0, data_bytes);
+    if (e == cudaSuccess) e = cudaMemset(p->v_data, 0, data_bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        ahpc_pool_destroy(p);
+        return fail(AHPC_COMPUTATION_FAILED, "ahpc_pool_create: initialisation failed: %s", cudaGetErrorString(e));
+    }
+    p->h_len.assign(c->max_seqs, 0);
+    p->h_pages.assign(c->max_seqs, 0);
+    p->h_shared.assign(c->max_seqs, 0);
+    p->h_live.assign(c->max_seqs, 0);
+    p->free_lower_bound = c->num_pages;
+    *out = p;
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_destroy(ahpc_pool* p) {
+    if (!p) return AHPC_SUCCESS;
+    if (cudaSetDevice(p->cfg.device) == cudaSuccess) {
+        (void)cudaDeviceSynchronize();
+        void* ptrs[] = {p->k_data, p->v_data, p->table, p->seq_len, p->seq_pages, p->refcount, p->ring, p->ctrl, p->call_args, p->scratch};
+        for (void* q : ptrs) if (q) (void)cudaFree(q);
+    }
+    (void)cudaGetLastError();
+    delete p;
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_seq_create(ahpc_pool* p, int32_t* seq_out) {
+    if (!p || !seq_out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_seq_create: NULL argument");
+    std::lock_guard<std::mutex> lock(p->mu);
+    for (int s = 0; s < p->cfg.max_seqs; ++s) {
+        if (!p->h_live[s]) {
+            p->h_live[s] = 1; p->h_len[s] = 0; p->h_pages[s] = 0; p->h_shared[s] = 0; p->live++;
+            *seq_out = s;
+            return AHPC_SUCCESS;
+        }
+    }
+    return fail(AHPC_MEMORY_ALLOCATION_FAILED, "ahpc_pool_seq_create: all %d sequence slots are in use", p->cfg.max_seqs);
+}
+
+ahpc_status ahpc_pool_seq_destroy(ahpc_pool* p, int32_t seq, void* stream) {
+    if (!p) return fail(AHPC_INVALID_INPUT, "ahpc_pool_seq_destroy: pool is NULL");
+    std::lock_guard<std::mutex> lock(p->mu);
+    AHPC_TRY(check_seq(p, seq, "ahpc_pool_seq_destroy"));
+    AHPC_TRY(use_device(p->cfg.device));
+    pool_release_kernel<<<1, ALLOC_THREADS, 0, (cudaStream_t)stream>>>(seq, 0, 0, 0, p->table, p->seq_len, p->seq_pages, p->refcount,
+                                                                        p->ring, p->ctrl, p->cfg.num_pages, p->cfg.max_pages_per_seq);
+    AHPC_CUDA_OK(cudaGetLastError());
+    p->free_lower_bound += p->h_pages[seq] - std::min(p->h_shared[seq], p->h_pages[seq]);
+    p->h_live[seq] = 0; p->h_len[seq] = 0; p->h_pages[seq] = 0; p->h_shared[seq] = 0; p->live--;
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_seq_truncate(ahpc_pool* p, int32_t seq, int32_t new_len, void* stream) {
+    if (!p) return fail(AHPC_INVALID_INPUT, "ahpc_pool_seq_truncate: pool is NULL");
+    std::lock_guard<std::mutex> lock(p->mu);
+    AHPC_TRY(check_seq(p, seq, "ahpc_pool_seq_truncate"));
+    if (new_len < 0) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_seq_truncate: negative length");
+    if (new_len >= p->h_len[seq]) return AHPC_SUCCESS;
+    AHPC_TRY(use_device(p->cfg.device));
+    const int keep = (new_len + p->cfg.page_size - 1) / p->cfg.page_size;
+    pool_release_kernel<<<1, ALLOC_THREADS, 0, (cudaStream_t)stream>>>(seq, keep, new_len, 1, p->table, p->seq_len, p->seq_pages,
+                                                                        p->refcount, p->ring, p->ctrl, p->cfg.num_pages,
+                                                                        p->cfg.max_pages_per_seq);
+    AHPC_CUDA_OK(cudaGetLastError());
+    const int dropped_from = std::max(keep, p->h_shared[seq]);           // pages below h_shared may still be held elsewhere
+    p->free_lower_bound += std::max(0, p->h_pages[seq] - dropped_from);
+    p->h_pages[seq] = keep;
+    p->h_shared[seq] = std::min(p->h_shared[seq], keep);
+    p->h_len[seq] = new_len;
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_seq_fork(ahpc_pool* p, int32_t src, int32_t n_prefix, int32_t* seq_out, void* stream) {
+    if (!p || !seq_out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_seq_fork: NULL argument");
+    std::lock_guard<std::mutex> lock(p->mu);
+    AHPC_TRY(check_seq(p, src, "ahpc_pool_seq_fork"));
+    if (n_prefix < 0 || n_prefix > p->h_len[src])
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_seq_fork: prefix %d exceeds the %d tokens of sequence %d", n_prefix, p->h_len[src], src);
+    AHPC_TRY(use_device(p->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int full = n_prefix / p->cfg.page_size, rem = n_prefix % p->cfg.page_size;
+    if (rem && p->free_lower_bound < 1) {
+        AHPC_TRY(refresh_free_count(p, st));
+        if (p->free_lower_bound < 1) return fail(AHPC_MEMORY_ALLOCATION_FAILED, "ahpc_pool_seq_fork: no free page");
+    }
+    int dst = -1;
+    for (int s = 0; s < p->cfg.max_seqs; ++s) if (!p->h_live[s]) { dst = s; break; }
+    if (dst < 0) return fail(AHPC_MEMORY_ALLOCATION_FAILED, "ahpc_pool_seq_fork: all %d sequence slots are in use", p->cfg.max_seqs);
+    pool_fork_kernel<<<1, ALLOC_THREADS, 0, st>>>(src, dst, full, rem, p->cfg.page_size, p->table, p->seq_len, p->seq_pages, p->refcount,
+                                                  p->ring, p->ctrl, p->cfg.num_pages, p->cfg.max_pages_per_seq);
+    AHPC_CUDA_OK(cudaGetLastError());
+    if (rem) {
+        const int pieces = p->cfg.head_dim / p->vec;
+        const int64_t work = (int64_t)rem * p->cfg.heads * pieces;
+        const int bx = (int)std::max<int64_t>(1, std::min<int64_t>((work + 255) / 256, 1024));
+        if (p->elem_size == 4)
+            pool_copy_partial_kernel<float><<<bx, 256, 0, st>>>((float*)p->k_data, (float*)p->v_data, p->table, src, dst, full, rem,
+                                                                p->cfg.heads, p->cfg.head_dim, p->cfg.page_size, p->cfg.max_pages_per_seq, p->page_elems);
+        else
+            pool_copy_partial_kernel<uint16_t><<<bx, 256, 0, st>>>((uint16_t*)p->k_data, (uint16_t*)p->v_data, p->table, src, dst, full, rem,
+                                                                   p->cfg.heads, p->cfg.head_dim, p->cfg.page_size, p->cfg.max_pages_per_seq, p->page_elems);
+        AHPC_CUDA_OK(cudaGetLastError());
+        p->free_lower_bound -= 1;
+    }
+    p->h_live[dst] = 1; p->live++;
+    p->h_len[dst] = n_prefix;
+    p->h_pages[dst] = full + (rem ? 1 : 0);
+    p->h_shared[dst] = full;
+    p->h_shared[src] = std::max(p->h_shared[src], full);
+    *seq_out = dst;
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_append(ahpc_pool* p, const int32_t* seqs, const int32_t* n_tokens, int32_t n, const void* k, const void* v,
+                             int32_t kv_dtype, void* stream) {
+    if (!p || !seqs || !n_tokens) return fail(AHPC_INVALID_INPUT, "ahpc_pool_append: NULL argument");
+    if (n <= 0) return AHPC_SUCCESS;
+    if (!dtype_valid(kv_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_append: unknown kv dtype %d", kv_dtype);
+    std::lock_guard<std::mutex> lock(p->mu);
+    if (n > p->cfg.max_seqs) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_append: %d sequences listed, pool holds %d", n, p->cfg.max_seqs);
+    cudaStream_t st = (cudaStream_t)stream;
+    AHPC_TRY(use_device(p->cfg.device));
+
+    std::vector<int32_t> host_args(3 * (size_t)n);
+    std::vector<uint8_t> listed(p->cfg.max_seqs, 0);
+    int64_t total_tokens = 0, total_need = 0;
+    int max_tokens = 0;
+    for (int i = 0; i < n; ++i) {
+        AHPC_TRY(check_seq(p, seqs[i], "ahpc_pool_append"));
+        if (listed[seqs[i]]) return fail(AHPC_INVALID_INPUT, "ahpc_pool_append: sequence %d listed twice", seqs[i]);
+        listed[seqs[i]] = 1;
+        if (n_tokens[i] < 0) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_append: negative token count");
+        const int64_t new_len = (int64_t)p->h_len[seqs[i]] + n_tokens[i];
+        const int64_t pages = (new_len + p->cfg.page_size - 1) / p->cfg.page_size;
+        if (pages > p->cfg.max_pages_per_seq)
+            return fail(AHPC_MEMORY_ALLOCATION_FAILED, "ahpc_pool_append: sequence %d would need %lld pages, the block table holds %d per sequence",
+                        seqs[i], (long long)pages, p->cfg.max_pages_per_seq);
+        total_need += std::max<int64_t>(0, pages - p->h_pages[seqs[i]]);
+        host_args[i] = seqs[i];
+        host_args[n + i] = n_tokens[i];
+        host_args[2 * (size_t)n + i] = (int32_t)total_tokens;
+        total_tokens += n_tokens[i];
+        max_tokens = std::max(max_tokens, n_tokens[i]);
+    }
+    if (total_tokens > 0 && (!k || !v)) return fail(AHPC_INVALID_INPUT, "ahpc_pool_append: k and v must not be NULL");
+    if (total_need > p->free_lower_bound) {
+        AHPC_TRY(refresh_free_count(p, st));
+        if (total_need > p->free_lower_bound)
+            return fail(AHPC_MEMORY_ALLOCATION_FAILED, "ahpc_pool_append: %lld pages needed, %lld free", (long long)total_need,
+                        (long long)p->free_lower_bound);
+    }
+    if (total_tokens == 0) return AHPC_SUCCESS;
+
+    const bool host_kv = is_host_pointer(k) || is_host_pointer(v);
+    const void *dk = k, *dv = v;
+    if (host_kv) {
+        const size_t bytes = (size_t)total_tokens * p->cfg.heads * p->cfg.head_dim * dtype_size(kv_dtype);
+        void *sk = nullptr, *sv = nullptr;
+        AHPC_TRY(staging_buffer(p->cfg.device, 5, bytes, &sk));
+        AHPC_TRY(staging_buffer(p->cfg.device, 6, bytes, &sv));
+        AHPC_CUDA_OK(cudaMemcpyAsync(sk, k, bytes, cudaMemcpyDefault, st));
+        AHPC_CUDA_OK(cudaMemcpyAsync(sv, v, bytes, cudaMemcpyDefault, st));
+        dk = sk; dv = sv;
+    }
+    AHPC_CUDA_OK(cudaMemcpyAsync(p->call_args, host_args.data(), host_args.size() * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    pool_append_alloc_kernel<<<1, ALLOC_THREADS, 0, st>>>(p->call_args, n, p->table, p->seq_len, p->seq_pages, p->refcount, p->ring, p->ctrl,
+                                                          p->cfg.num_pages, p->cfg.page_size, p->cfg.max_pages_per_seq);
+    AHPC_CUDA_OK(cudaGetLastError());
+    ahpc_status s;
+    if (p->cfg.dtype == AHPC_F32) s = scatter_dispatch<float>(p, dk, dv, kv_dtype, n, max_tokens, st);
+    else if (p->cfg.dtype == AHPC_F16) s = scatter_dispatch<__half>(p, dk, dv, kv_dtype, n, max_tokens, st);
+    else s = scatter_dispatch<__nv_bfloat16>(p, dk, dv, kv_dtype, n, max_tokens, st);
+    AHPC_TRY(s);
+    for (int i = 0; i < n; ++i) {
+        const int sq = seqs[i];
+        p->h_len[sq] += n_tokens[i];
+        p->h_pages[sq] = std::max(p->h_pages[sq], (p->h_len[sq] + p->cfg.page_size - 1) / p->cfg.page_size);
+    }
+    p->free_lower_bound -= total_need;
+    // host_args is pageable: cudaMemcpyAsync has already staged it when it returned.  Host K/V
+    // follow the library's rule for host tensors: the call completes before it returns.
+    if (host_kv) AHPC_CUDA_OK(cudaStreamSynchronize(st));
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_gather(ahpc_pool* p, int32_t seq, int32_t start, int32_t n, void* k_out, void* v_out, int32_t out_dtype, void* stream) {
+    if (!p || !k_out || !v_out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_gather: NULL argument");
+    if (!dtype_valid(out_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_gather: unknown dtype %d", out_dtype);
+    std::lock_guard<std::mutex> lock(p->mu);
+    AHPC_TRY(check_seq(p, seq, "ahpc_pool_gather"));
+    if (start < 0 || n < 0 || (int64_t)start + n > p->h_len[seq])
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_gather: tokens [%d, %d) outside sequence of %d", start, start + n, p->h_len[seq]);
+    if (n == 0) return AHPC_SUCCESS;
+    AHPC_TRY(use_device(p->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool host_out = is_host_pointer(k_out) || is_host_pointer(v_out);
+    const size_t bytes = (size_t)n * p->cfg.heads * p->cfg.head_dim * dtype_size(out_dtype);
+    void *dk = k_out, *dv = v_out;
+    if (host_out) {
+        AHPC_TRY(staging_buffer(p->cfg.device, 5, bytes, &dk));
+        AHPC_TRY(staging_buffer(p->cfg.device, 6, bytes, &dv));
+    }
+    ahpc_status s;
+    if (p->cfg.dtype == AHPC_F32) s = gather_dispatch<float>(p, dk, dv, out_dtype, seq, start, n, st);
+    else if (p->cfg.dtype == AHPC_F16) s = gather_dispatch<__half>(p, dk, dv, out_dtype, seq, start, n, st);
+    else s = gather_dispatch<__nv_bfloat16>(p, dk, dv, out_dtype, seq, start, n, st);
+    AHPC_TRY(s);
+    if (host_out) {
+        AHPC_CUDA_OK(cudaMemcpyAsync(k_out, dk, bytes, cudaMemcpyDefault, st));
+        AHPC_CUDA_OK(cudaMemcpyAsync(v_out, dv, bytes, cudaMemcpyDefault, st));
+        AHPC_CUDA_OK(cudaStreamSynchronize(st));
+    }
+    return AHPC_SUCCESS;
+}
+
+int32_t ahpc_pool_seq_len(const ahpc_pool* p, int32_t seq) {
+    if (!p || seq < 0 || seq >= p->cfg.max_seqs || !p->h_live[seq]) return -1;
+    return p->h_len[seq];
+}
+int32_t ahpc_pool_seq_pages(const ahpc_pool* p, int32_t seq) {
+    if (!p || seq < 0 || seq >= p->cfg.max_seqs || !p->h_live[seq]) return -1;
+    return p->h_pages[seq];
+}
+int64_t ahpc_pool_free_pages(const ahpc_pool* p) { return p ? p->free_lower_bound : 0; }
+int64_t ahpc_pool_page_bytes(const ahpc_pool* p) { return p ? (int64_t)(2 * p->page_elems * p->elem_size) : 0; }
+int32_t ahpc_pool_live_seqs(const ahpc_pool* p) { return p ? p->live : 0; }
+
+ahpc_status ahpc_pool_read_block_table(ahpc_pool* p, int32_t seq, int32_t* out, int32_t n, void* stream) {
+    if (!p || !out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_block_table: NULL argument");
+    if (seq < 0 || seq >= p->cfg.max_seqs) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_block_table: sequence %d out of range", seq);
+    if (n < 0 || n > p->cfg.max_pages_per_seq) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_read_block_table: n out of range");
+    AHPC_TRY(use_device(p->cfg.device));
+    AHPC_CUDA_OK(cudaMemcpyAsync(out, p->table + (size_t)seq * p->cfg.max_pages_per_seq, n * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    AHPC_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_read_seq_lens(ahpc_pool* p, int32_t* out, int32_t n, void* stream) {
+    if (!p || !out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_seq_lens: NULL argument");
+    if (n < 0 || n > p->cfg.max_seqs) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_read_seq_lens: n out of range");
+    AHPC_TRY(use_device(p->cfg.device));
+    AHPC_CUDA_OK(cudaMemcpyAsync(out, p->seq_len, n * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    AHPC_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_read_refcounts(ahpc_pool* p, int32_t* out, int32_t n, void* stream) {
+    if (!p || !out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_refcounts: NULL argument");
+    if (n < 0 || n > p->cfg.num_pages) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_read_refcounts: n out of range");
+    AHPC_TRY(use_device(p->cfg.device));
+    AHPC_CUDA_OK(cudaMemcpyAsync(out, p->refcount, n * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    AHPC_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_read_free_ring(ahpc_pool* p, int32_t* out, int32_t n, int64_t* count_out, void* stream) {
+    if (!p || !count_out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_free_ring: NULL argument");
+    AHPC_TRY(use_device(p->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    long long c[4];
+    AHPC_CUDA_OK(cudaMemcpyAsync(c, p->ctrl, sizeof(c), cudaMemcpyDeviceToHost, st));
+    std::vector<int32_t> ring(p->cfg.num_pages);
+    AHPC_CUDA_OK(cudaMemcpyAsync(ring.data(), p->ring, ring.size() * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    AHPC_CUDA_OK(cudaStreamSynchronize(st));
+    *count_out = c[CTRL_COUNT];
+    {
+        std::lock_guard<std::mutex> lock(p->mu);
+        p->free_lower_bound = c[CTRL_COUNT];
+    }
+    if (out)
+        for (int64_t i = 0; i < c[CTRL_COUNT] && i < n; ++i) out[i] = ring[(c[CTRL_HEAD] + i) % p->cfg.num_pages];
+    return AHPC_SUCCESS;
+}
+
+ahpc_status ahpc_pool_read_error_flag(ahpc_pool* p, int32_t* out, void* stream) {
+    if (!p || !out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_error_flag: NULL argument");
+    AHPC_TRY(use_device(p->cfg.device));
+    long long c[4];
+    AHPC_CUDA_OK(cudaMemcpyAsync(c, p->ctrl, sizeof(c), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    AHPC_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+    *out = (int32_t)c[CTRL_ERROR];
+    return AHPC_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,434 @@
+// PagedAttention decode: one query token per sequence attends to every token the sequence holds
+// in the paged KV pool.
+//
+// Replaces PagedAttention::forward_batch / compute_paged_attention
+// (src/algorithms/paged_attention.cpp:496-547, 596-680: per sequence and head, gather the whole
+// context, dot, softmax, weighted sum) and paged_attention_kernel (src/backends/cuda/cuda_kernels.cu:
+// 370-515: walk page_table[b][p], stop at an entry < 0, online softmax per page).
+//
+// This is a streaming kernel: 1 FLOP per byte, bounded by HBM bandwidth.  No tensor cores.
+//   split-KV (flash-decoding): a sequence is cut into chunks of `split` tokens; the grid is
+//   (chunk, head, sequence); every CTA writes an unnormalised partial output with its running
+//   (max, sum) in base-2 log units, and a second small kernel merges a sequence's partials.
+//   Inside a CTA each of the 4 warps takes whole pages.  Keys are stored slot-interleaved
+//   (see pool.cuh) so one 16-byte load per lane brings 8 dims of the key owned by that lane: a
+//   lane finishes a whole q.k product with a single cross-lane add.  Values are rows; a lane owns
+//   8 output dims and gets the softmax weight of a slot by one shuffle.
+#include <cmath>
+#include <cstdlib>
+
+#include <algorithm>
+
+#include "pool.cuh"
+
+namespace ahpc {
+namespace {
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct DecodeParams {
+    const void* q;             // [n_seqs][heads][head_dim] of TQ
+    void* out;
+    const void* k_data;
+    const void* v_data;
+    const int32_t* table;
+    const int32_t* seq_len;
+    const int32_t* seqs;       // device copy of the call's sequence slots
+    float* part_o;             // [n_seqs][max_chunks][heads][head_dim]
+    float2* part_ml;           // [n_seqs][max_chunks][heads]  (max, sum), base-2
+    int n_seqs, heads, head_dim, page_size, max_pages, max_chunks, split;
+    size_t page_elems;
+    float scale_log2;          // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
+template <typename T> struct Pair;
+template <> struct Pair<__half> {
+    static __device__ __forceinline__ float2 unpack(uint32_t u) { return __half22float2(*reinterpret_cast<const __half2*>(&u)); }
+};
+template <> struct Pair<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 unpack(uint32_t u) {
+        return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+    }
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+    float2 a = Pair<T>::unpack(u.x), b = Pair<T>::unpack(u.y), c = Pair<T>::unpack(u.z), d = Pair<T>::unpack(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+// Fast path: 16-bit pool, page size 16, head_dim D in {64, 128}.
+template <typename T, typename TQ, int D>
+__global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(const DecodeParams p) {
+    constexpr int PAGE = 16;
+    constexpr int PIECES = D / 8;            // 16-byte pieces per key / value row
+    constexpr int KP = PIECES / 2;           // key pieces per lane (each half-warp takes half of them)
+    constexpr int LPR = PIECES;              // lanes that cover one value row
+    constexpr int GROUPS = 32 / LPR;         // value rows read per warp-wide load
+    constexpr int SPG = PAGE / GROUPS;       // slots per group
+
+    const int chunk = blockIdx.x, head = blockIdx.y, si = blockIdx.z;
+    const int seq = p.seqs[si];
+    const int len = p.seq_len[seq];
+    const int tok0 = chunk * p.split;
+    if (tok0 >= len) return;
+    const int tok1 = min(len, tok0 + p.split);
+    const int page0 = tok0 / PAGE, n_pages = (tok1 - tok0 + PAGE - 1) / PAGE;
+
+    __shared__ __align__(16) float q_s[D];
+    __shared__ float sm_acc[DEC_WARPS][D];
+    __shared__ float sm_m[DEC_WARPS], sm_l[DEC_WARPS];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int d = tid; d < D; d += DEC_THREADS)
+        q_s[d] = to_f32<TQ>(static_cast<const TQ*>(p.q)[((size_t)si * p.heads + head) * D + d]) * p.scale_log2;
+    __syncthreads();
+
+    const int slot = lane & 15, half = lane >> 4;            // key phase: lane owns key `slot`
+    const int vcol = lane % LPR, vgrp = lane / LPR;          // value phase: lane owns dims [8*vcol, 8*vcol+8)
+    const T* kbase = static_cast<const T*>(p.k_data);
+    const T* vbase = static_cast<const T*>(p.v_data);
+    const int32_t* row = p.table + (size_t)seq * p.max_pages;
+
+    float m_run = -INFINITY, l_part = 0.f, acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+
+    for (int pi = warp; pi < n_pages; pi += DEC_WARPS) {
+        const int page = row[page0 + pi];
+        if (page < 0) break;                                  // table shorter than the length says: stop (cuda_kernels.cu:419-420)
+        const size_t pbase = (size_t)page * p.page_elems + (size_t)head * PAGE * D;
+        uint4 kreg[KP], vreg[SPG];
+#pragma unroll
+        for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)(half * KP + j) * PAGE + slot) * 8);
+#pragma unroll
+        for (int i = 0; i < SPG; ++i) vreg[i] = ld_stream(vbase + pbase + (size_t)(vgrp * SPG + i) * D + vcol * 8);
+
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < KP; ++j) {
+            float kf[8];
+            unpack8<T>(kreg[j], kf);
+            const float4 qa = *reinterpret_cast<const float4*>(&q_s[(half * KP + j) * 8]);
+            const float4 qb = *reinterpret_cast<const float4*>(&q_s[(half * KP + j) * 8 + 4]);
+            s = fmaf(kf[0], qa.x, s); s = fmaf(kf[1], qa.y, s); s = fmaf(kf[2], qa.z, s); s = fmaf(kf[3], qa.w, s);
+            s = fmaf(kf[4], qb.x, s); s = fmaf(kf[5], qb.y, s); s = fmaf(kf[6], qb.z, s); s = fmaf(kf[7], qb.w, s);
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 16);
+        if (tok0 + pi * PAGE + slot >= tok1) s = -INFINITY;
+        float pm = s;
+#pragma unroll
+        for (int off = 8; off >= 1; off >>= 1) pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, off));
+        if (pm > m_run) {                                     // warp-uniform
+            const float alpha = exp2f(m_run - pm);            // m_run = -inf gives 0
+            l_part *= alpha;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] *= alpha;
+            m_run = pm;
+        }
+        const float w = (s == -INFINITY) ? 0.f : exp2f(s - m_run);
+        l_part += w;
+#pragma unroll
+        for (int i = 0; i < SPG; ++i) {
+            const float wi = __shfl_sync(0xffffffffu, w, vgrp * SPG + i);
+            float vf[8];
+            unpack8<T>(vreg[i], vf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(wi, vf[e], acc[e]);
+        }
+    }
+
+    // fold the value-row groups of the warp, and the per-slot sums of lanes 0..15
+#pragma unroll
+    for (int off = 16; off >= LPR; off >>= 1)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+    float l_warp = l_part;
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) l_warp += __shfl_xor_sync(0xffffffffu, l_warp, off);
+    if (lane < LPR) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sm_acc[warp][lane * 8 + e] = acc[e];
+    }
+    if (lane == 0) { sm_m[warp] = m_run; sm_l[warp] = l_warp; }
+    __syncthreads();
+
+    float m_all = sm_m[0];
+#pragma unroll
+    for (int w = 1; w < DEC_WARPS; ++w) m_all = fmaxf(m_all, sm_m[w]);
+    const size_t pidx = ((size_t)si * p.max_chunks + chunk) * p.heads + head;
+    for (int d = tid; d < D; d += DEC_THREADS) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) o += sm_acc[w][d] * exp2f(sm_m[w] - m_all);
+        p.part_o[pidx * D + d] = o;
+    }
+    if (tid == 0) {
+        float l = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) l += sm_l[w] * exp2f(sm_m[w] - m_all);
+        p.part_ml[pidx] = make_float2(m_all, l);
+    }
+}
+
+// General path: any pool type, page size and head_dim (multiple of the 16-byte piece).  One CTA per
+// (chunk, head, sequence): scores of the chunk into shared memory (a thread per token), block-wide
+// max and sum, then a thread per output dim.  split <= GEN_MAX_SPLIT.
+constexpr int GEN_MAX_SPLIT = 2048;
+
+template <typename T, typename TQ>
+__global__ void __launch_bounds__(DEC_THREADS) paged_decode_generic_kernel(const DecodeParams p) {
+    constexpr int VEC = 16 / sizeof(T);
+    extern __shared__ float gsm[];
+    float* q_s = gsm;                       // [head_dim]
+    float* sc = gsm + p.head_dim;           // [split]
+    __shared__ float red[DEC_WARPS];
+
+    const int chunk = blockIdx.x, head = blockIdx.y, si = blockIdx.z;
+    const int seq = p.seqs[si];
+    const int len = p.seq_len[seq];
+    const int tok0 = chunk * p.split;
+    if (tok0 >= len) return;
+    const int tok1 = min(len, tok0 + p.split), nt = tok1 - tok0;
+    const int D = p.head_dim, PS = p.page_size;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const T* kbase = static_cast<const T*>(p.k_data);
+    const T* vbase = static_cast<const T*>(p.v_data);
+    const int32_t* row = p.table + (size_t)seq * p.max_pages;
+
+    for (int d = tid; d < D; d += DEC_THREADS)
+        q_s[d] = to_f32<TQ>(static_cast<const TQ*>(p.q)[((size_t)si * p.heads + head) * D + d]) * p.scale_log2;
+    __syncthreads();
+
+    float m_loc = -INFINITY;
+    for (int t = tid; t < nt; t += DEC_THREADS) {
+        const int pos = tok0 + t;
+        const int page = row[pos / PS];
+        float s = -INFINITY;
+        if (page >= 0) {
+            s = 0.f;
+            for (int piece = 0; piece < D / VEC; ++piece) {
+                const T* kp = kbase + k_piece_offset(p.page_elems, p.heads, PS, D, VEC, page, head, pos % PS, piece);
+                for (int e = 0; e < VEC; ++e) s = fmaf(to_f32<T>(kp[e]), q_s[piece * VEC + e], s);
+            }
+        }
+        sc[t] = s;
+        m_loc = fmaxf(m_loc, s);
+    }
+    for (int off = 16; off >= 1; off >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, off));
+    if (lane == 0) red[warp] = m_loc;
+    __syncthreads();
+    float m_all = red[0];
+    for (int w = 1; w < DEC_WARPS; ++w) m_all = fmaxf(m_all, red[w]);
+    __syncthreads();
+    float l_loc = 0.f;
+    for (int t = tid; t < nt; t += DEC_THREADS) {
+        const float w = (sc[t] == -INFINITY) ? 0.f : exp2f(sc[t] - m_all);
+        sc[t] = w;
+        l_loc += w;
+    }
+    for (int off = 16; off >= 1; off >>= 1) l_loc += __shfl_xor_sync(0xffffffffu, l_loc, off);
+    if (lane == 0) red[warp] = l_loc;
+    __syncthreads();
+    const size_t pidx = ((size_t)si * p.max_chunks + chunk) * p.heads + head;
+    for (int d = tid; d < D; d += DEC_THREADS) {
+        float o = 0.f;
+        for (int t = 0; t < nt; ++t) {
+            const int pos = tok0 + t;
+            const int page = row[pos / PS];
+            if (page < 0) break;
+            o = fmaf(sc[t], to_f32<T>(vbase[v_row_offset(p.page_elems, PS, D, page, head, pos % PS) + d]), o);
+        }
+        p.part_o[pidx * D + d] = o;
+    }
+    if (tid == 0) {
+        float l = 0.f;
+        for (int w = 0; w < DEC_WARPS; ++w) l += red[w];
+        p.part_ml[pidx] = make_float2(m_all, l);
+    }
+}
+
+// Merge of a sequence's chunk partials (the log-sum-exp combine).  grid (heads, n_seqs).
+template <typename TQ>
+__global__ void paged_combine_kernel(const DecodeParams p) {
+    const int head = blockIdx.x, si = blockIdx.y;
+    const int seq = p.seqs[si];
+    const int len = p.seq_len[seq];
+    const int n_chunks = (len + p.split - 1) / p.split;
+    const int D = p.head_dim;
+    const size_t base = (size_t)si * p.max_chunks * p.heads + head;
+    float m_all = -INFINITY;
+    for (int c = 0; c < n_chunks; ++c) m_all = fmaxf(m_all, p.part_ml[base + (size_t)c * p.heads].x);
+    float l = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+        const float2 ml = p.part_ml[base + (size_t)c * p.heads];
+        l += (ml.x == -INFINITY) ? 0.f : ml.y * exp2f(ml.x - m_all);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;            // empty sequence: zeros
+    TQ* out = static_cast<TQ*>(p.out) + ((size_t)si * p.heads + head) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float o = 0.f;
+        for (int c = 0; c < n_chunks; ++c) {
+            const float2 ml = p.part_ml[base + (size_t)c * p.heads];
+            if (ml.x == -INFINITY) continue;
+            o += p.part_o[(base + (size_t)c * p.heads) * D + d] * exp2f(ml.x - m_all);
+        }
+        out[d] = from_f32<TQ>(o * inv);
+    }
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct ScratchLayout { size_t seqs_off, ml_off, o_off, total; };
+ScratchLayout scratch_layout(int n_seqs, int max_chunks, int heads, int head_dim) {
+    ScratchLayout s;
+    s.seqs_off = 0;
+    s.ml_off = align_up((size_t)n_seqs * sizeof(int32_t), 256);
+    s.o_off = s.ml_off + align_up((size_t)n_seqs * max_chunks * heads * sizeof(float2), 256);
+    s.total = s.o_off + (size_t)n_seqs * max_chunks * heads * head_dim * sizeof(float);
+    return s;
+}
+
+bool fast_path(const ahpc_pool* p) {
+    return p->cfg.dtype != AHPC_F32 && p->cfg.page_size == 16 && (p->cfg.head_dim == 64 || p->cfg.head_dim == 128);
+}
+
+int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, int sms) {
+    const int ps = p->cfg.page_size;
+    if (requested > 0) return requested;
+    int split = std::max(ps, 512 / ps * ps);
+    // Halve the chunk until the grid holds a few CTAs per SM slot (8 CTAs of 128 threads fit an SM).
+    while (split / 2 >= 64 && (split / 2) % ps == 0) {
+        int64_t ctas = 0;
+        for (int i = 0; i < n; ++i) ctas += (p->h_len[seqs[i]] + split - 1) / split;
+        ctas *= p->cfg.heads;
+        if (ctas >= (int64_t)sms * 16) break;
+        split /= 2;
+    }
+    return split;
+}
+
+template <typename T, typename TQ>
+ahpc_status launch_decode(const ahpc_pool* pool, const DecodeParams& dp, cudaStream_t st) {
+    dim3 grid(dp.max_chunks, dp.heads, dp.n_seqs);
+    bool launched = false;
+    if constexpr (sizeof(T) == 2) {
+        if (fast_path(pool)) {
+            if (dp.head_dim == 128) paged_decode_kernel<T, TQ, 128><<<grid, DEC_THREADS, 0, st>>>(dp);
+            else paged_decode_kernel<T, TQ, 64><<<grid, DEC_THREADS, 0, st>>>(dp);
+            launched = true;
+        }
+    }
+    if (!launched) {
+        size_t smem = (size_t)(dp.head_dim + dp.split) * sizeof(float);
+        paged_decode_generic_kernel<T, TQ><<<grid, DEC_THREADS, smem, st>>>(dp);
+    }
+    AHPC_CUDA_OK(cudaGetLastError());
+    paged_combine_kernel<TQ><<<dim3(dp.heads, dp.n_seqs), std::min(128, (dp.head_dim + 31) / 32 * 32), 0, st>>>(dp);
+    AHPC_CUDA_OK(cudaGetLastError());
+    return AHPC_SUCCESS;
+}
+
+template <typename T>
+ahpc_status launch_decode_q(const ahpc_pool* pool, const DecodeParams& dp, int qo_dtype, cudaStream_t st) {
+    switch (qo_dtype) {
+        case AHPC_F32: return launch_decode<T, float>(pool, dp, st);
+        case AHPC_F16: return launch_decode<T, __half>(pool, dp, st);
+        case AHPC_BF16: return launch_decode<T, __nv_bfloat16>(pool, dp, st);
+    }
+    return fail(AHPC_INVALID_PARAMETERS, "unknown q/out dtype %d", qo_dtype);
+}
+
+}  // namespace
+}  // namespace ahpc
+
+using namespace ahpc;
+
+extern "C" {
+
+size_t ahpc_paged_decode_scratch_bytes(const ahpc_pool* p, int32_t n_seqs, int32_t max_len, int32_t split_tokens) {
+    if (!p || n_seqs <= 0) return 0;
+    int split = split_tokens > 0 ? split_tokens : 64;      // the smallest chunk the library picks on its own
+    int max_chunks = std::max(1, (max_len + split - 1) / split);
+    return scratch_layout(n_seqs, max_chunks, p->cfg.heads, p->cfg.head_dim).total;
+}
+
+ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
+    if (!a || !a->pool) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode: NULL argument");
+    ahpc_pool* p = a->pool;
+    if (a->n_seqs <= 0) return AHPC_SUCCESS;
+    if (!a->seqs || !a->q || !a->out) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode: seqs, q and out must not be NULL");
+    if (!dtype_valid(a->qo_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: unknown dtype %d", a->qo_dtype);
+    if (a->n_seqs > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode: at most 65535 sequences per call");
+    if (p->cfg.heads > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode: at most 65535 heads");
+    std::lock_guard<std::mutex> lock(p->mu);
+    AHPC_TRY(use_device(p->cfg.device));
+    cudaStream_t st = (cudaStream_t)a->stream;
+    int max_len = 0;
+    for (int i = 0; i < a->n_seqs; ++i) {
+        const int s = a->seqs[i];
+        if (s < 0 || s >= p->cfg.max_seqs || !p->h_live[s]) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode: sequence %d not found", s);
+        max_len = std::max(max_len, p->h_len[s]);
+    }
+    const int ps = p->cfg.page_size;
+    int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device));
+    if (split % ps) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: split_tokens %d is not a multiple of the page size %d", split, ps);
+    if (!fast_path(p) && split > GEN_MAX_SPLIT)
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: split_tokens %d exceeds %d for this pool configuration", split, GEN_MAX_SPLIT);
+    const int max_chunks = std::max(1, (max_len + split - 1) / split);
+    if (max_chunks > 2147483647 / 1) return fail(AHPC_INTERNAL_ERROR, "ahpc_paged_decode: chunk count overflow");
+
+    const ScratchLayout lay = scratch_layout(a->n_seqs, max_chunks, p->cfg.heads, p->cfg.head_dim);
+    if (p->scratch_bytes < lay.total) {
+        if (p->scratch) { AHPC_CUDA_OK(cudaStreamSynchronize(st)); AHPC_CUDA_OK(cudaFree(p->scratch)); p->scratch = nullptr; p->scratch_bytes = 0; }
+        size_t want = align_up(lay.total, size_t(1) << 20);
+        AHPC_CUDA_OK(cudaMalloc(&p->scratch, want));
+        p->scratch_bytes = want;
+    }
+    char* sc = static_cast<char*>(p->scratch);
+
+    const size_t qo_bytes = (size_t)a->n_seqs * p->cfg.heads * p->cfg.head_dim * dtype_size(a->qo_dtype);
+    const bool host_q = is_host_pointer(a->q), host_o = is_host_pointer(a->out);
+    const void* dq = a->q;
+    void* dout = a->out;
+    if (host_q) {
+        void* s = nullptr;
+        AHPC_TRY(staging_buffer(p->cfg.device, 7, qo_bytes, &s));
+        AHPC_CUDA_OK(cudaMemcpyAsync(s, a->q, qo_bytes, cudaMemcpyHostToDevice, st));
+        dq = s;
+    }
+    if (host_o) AHPC_TRY(staging_buffer(p->cfg.device, 8, qo_bytes, &dout));
+    AHPC_CUDA_OK(cudaMemcpyAsync(sc + lay.seqs_off, a->seqs, (size_t)a->n_seqs * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+
+    DecodeParams dp;
+    dp.q = dq; dp.out = dout; dp.k_data = p->k_data; dp.v_data = p->v_data;
+    dp.table = p->table; dp.seq_len = p->seq_len;
+    dp.seqs = reinterpret_cast<const int32_t*>(sc + lay.seqs_off);
+    dp.part_ml = reinterpret_cast<float2*>(sc + lay.ml_off);
+    dp.part_o = reinterpret_cast<float*>(sc + lay.o_off);
+    dp.n_seqs = a->n_seqs; dp.heads = p->cfg.heads; dp.head_dim = p->cfg.head_dim; dp.page_size = ps;
+    dp.max_pages = p->cfg.max_pages_per_seq; dp.max_chunks = max_chunks; dp.split = split;
+    dp.page_elems = p->page_elems;
+    const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);
+    dp.scale_log2 = scale * LOG2E;
+
+    ahpc_status s;
+    if (p->cfg.dtype == AHPC_F32) s = launch_decode_q<float>(p, dp, a->qo_dtype, st);
+    else if (p->cfg.dtype == AHPC_F16) s = launch_decode_q<__half>(p, dp, a->qo_dtype, st);
+    else s = launch_decode_q<__nv_bfloat16>(p, dp, a->qo_dtype, st);
+    AHPC_TRY(s);
+    if (host_o) AHPC_CUDA_OK(cudaMemcpyAsync(a->out, dout, qo_bytes, cudaMemcpyDeviceToHost, st));
+    if (host_q || host_o) AHPC_CUDA_OK(cudaStreamSynchronize(st));
+    return AHPC_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,69 @@
+// Paged KV pool: what lives where.
+//
+// In HBM (written only by kernels of kv_pool.cu):
+//   k_data   [num_pages][heads][head_dim/VEC][page_size][VEC]   VEC = 16 bytes / sizeof(element)
+//            keys, "slot-interleaved": the 16-byte pieces of one key are page_size*16 bytes apart,
+//            so that 16 consecutive lanes reading piece j of 16 consecutive slots touch one
+//            contiguous 256-byte run and every lane ends up owning one whole key.
+//   v_data   [num_pages][heads][page_size][head_dim]
+//            values, row per slot: a lane owns 16 bytes of the head dimension of every slot.
+//   table    int32 [max_seqs][max_pages]   block table, -1 = no page
+//   seq_len  int32 [max_seqs]              tokens held
+//   seq_pages int32 [max_seqs]             pages held
+//   refcount int32 [num_pages]
+//   ring     int32 [num_pages]             FIFO of free page ids
+//   ctrl     int64 [4]                     {ring head, ring count, error flag, unused}
+//
+// On the host (struct ahpc_pool): the configuration, a mirror of seq_len / seq_pages / live flags,
+// and a LOWER BOUND of the number of free pages (exact unless pages are shared between sequences;
+// refreshed from the device when an allocation would otherwise be refused).
+#pragma once
+
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+struct ahpc_pool {
+    ahpc_pool_config cfg{};
+    int vec = 8;                       // elements per 16-byte piece
+    size_t elem_size = 2;
+    size_t page_elems = 0;             // elements of K (or V) in one page: heads * page_size * head_dim
+
+    void* k_data = nullptr;
+    void* v_data = nullptr;
+    int32_t* table = nullptr;
+    int32_t* seq_len = nullptr;
+    int32_t* seq_pages = nullptr;
+    int32_t* refcount = nullptr;
+    int32_t* ring = nullptr;
+    long long* ctrl = nullptr;
+    int32_t* call_args = nullptr;      // device copy of the per-call host arrays (4 * max_seqs + 8 ints)
+
+    // split-KV scratch of the decode path, grown on demand
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+
+    std::mutex mu;
+    std::vector<int32_t> h_len, h_pages, h_shared;   // h_shared: leading pages that may be shared
+    std::vector<uint8_t> h_live;
+    int64_t free_lower_bound = 0;
+    int32_t live = 0;
+};
+
+namespace ahpc {
+
+enum PoolCtrl { CTRL_HEAD = 0, CTRL_COUNT = 1, CTRL_ERROR = 2 };
+
+// Element offset of piece `piece` (VEC elements) of key `slot` of (page, head).
+__host__ __device__ inline size_t k_piece_offset(size_t page_elems, int heads, int page_size, int head_dim, int vec,
+                                                 int page, int head, int slot, int piece) {
+    (void)heads;
+    return (size_t)page * page_elems + (size_t)head * page_size * head_dim + ((size_t)piece * page_size + slot) * vec;
+}
+// Element offset of value row `slot` of (page, head).
+__host__ __device__ inline size_t v_row_offset(size_t page_elems, int page_size, int head_dim, int page, int head, int slot) {
+    return (size_t)page * page_elems + ((size_t)head * page_size + slot) * head_dim;
+}
+
+}  // namespace ahpc

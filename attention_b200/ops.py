@@ -1,0 +1,214 @@
+"""torch-tensor front end of the C ABI, used by the tests and the benchmark.
+
+torch supplies device memory and streams only; all arithmetic happens in the native library.
+Tensors may live on the GPU (the call enqueues on torch's current stream) or on the CPU (the
+library stages them through the device and returns when the result is back).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import abi
+
+_DTYPE = {torch.float32: abi.F32, torch.float16: abi.F16, torch.bfloat16: abi.BF16}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _stream_for(*tensors) -> tuple[int, int]:
+    """(device ordinal, cudaStream_t) for a call touching these tensors."""
+    dev = None
+    for t in tensors:
+        if t is not None and t.is_cuda:
+            dev = t.device.index
+            break
+    if dev is None:
+        dev = torch.cuda.current_device() if torch.cuda.is_available() else 0
+    stream = torch.cuda.current_stream(dev).cuda_stream if torch.cuda.is_available() else 0
+    return dev, stream
+
+
+def flash_attention_forward(q, k, v, *, causal=False, scale=0.0, mask=None, out=None, lse=None,
+                            kernel=abi.KERNEL_AUTO, device=None):
+    """out[b,h,i,:] = softmax_j(scale * q[b,h,i,:].k[b,h,j,:] + masks) . v[b,h,j,:]
+
+    q, k, v: tensors indexed [B, H, S, D] (any strides: pass `x.permute(0, 2, 1, 3)` for data stored
+    [B, S, H, D]).  mask: optional float32 [B, Sq, Skv], 0 = masked.  Returns `out` (allocated like q
+    when not given)."""
+    assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4
+    B, H, Sq, D = q.shape
+    Skv = k.shape[2]
+    if out is None:
+        out = torch.empty_strided(q.shape, q.stride(), dtype=q.dtype, device=q.device)
+    a = abi.FaArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    if mask is not None:
+        assert mask.dtype == torch.float32 and mask.is_contiguous() and tuple(mask.shape) == (B, Sq, Skv)
+        a.mask = mask.data_ptr()
+    if lse is not None:
+        assert lse.dtype == torch.float32 and lse.is_contiguous() and tuple(lse.shape) == (B, H, Sq)
+        a.lse = lse.data_ptr()
+    a.dtype = _dtype_code(q)
+    a.batch, a.heads, a.seq_q, a.seq_kv, a.head_dim = B, H, Sq, Skv, D
+    a.q_strides = (C.c_int64 * 4)(*q.stride())
+    a.k_strides = (C.c_int64 * 4)(*k.stride())
+    a.v_strides = (C.c_int64 * 4)(*v.stride())
+    a.o_strides = (C.c_int64 * 4)(*out.stride())
+    a.scale, a.causal, a.kernel = float(scale), int(bool(causal)), int(kernel)
+    dev, stream = _stream_for(q, k, v, out)
+    a.device = dev if device is None else device
+    a.stream = stream
+    abi.check(abi.lib().ahpc_fa_fwd(C.byref(a)))
+    return out
+
+
+def select_kernel(q, k, *, mask=None, kernel=abi.KERNEL_AUTO) -> int:
+    """Which kernel the library would run for tensors shaped like these."""
+    a = abi.FaArgs()
+    a.q = a.k = a.v = a.out = 1  # only shapes matter here
+    a.mask = 1 if mask is not None else None
+    a.dtype = _dtype_code(q)
+    a.batch, a.heads, a.seq_q, a.head_dim = q.shape
+    a.seq_kv = k.shape[2]
+    a.q_strides = a.o_strides = (C.c_int64 * 4)(*q.stride())
+    a.k_strides = a.v_strides = (C.c_int64 * 4)(*k.stride())
+    a.kernel = kernel
+    return abi.lib().ahpc_fa_select_kernel(C.byref(a))
+
+
+def _i32(values) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(values, dtype=np.int32).reshape(-1))
+
+
+def _pi32(a: np.ndarray):
+    return a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+class KVPool:
+    """A paged KV pool on one device (include/ahpc.h: ahpc_pool_*) plus the decode entry point."""
+
+    def __init__(self, *, num_pages, heads, head_dim, dtype=torch.float16, page_size=16, max_seqs=64,
+                 max_pages_per_seq=1024, device=0, free_order=None):
+        cfg = abi.PoolConfig()
+        cfg.device, cfg.dtype = device, _DTYPE[dtype]
+        cfg.num_pages, cfg.page_size, cfg.heads, cfg.head_dim = num_pages, page_size, heads, head_dim
+        cfg.max_seqs, cfg.max_pages_per_seq = max_seqs, max_pages_per_seq
+        self._order = None
+        if free_order is not None:
+            self._order = _i32(free_order)
+            cfg.free_order = _pi32(self._order)
+        self._p = C.c_void_p()
+        abi.check(abi.lib().ahpc_pool_create(C.byref(self._p), C.byref(cfg)))
+        self.device, self.dtype, self.num_pages, self.page_size = device, dtype, num_pages, page_size
+        self.heads, self.head_dim, self.max_seqs, self.max_pages_per_seq = heads, head_dim, max_seqs, max_pages_per_seq
+
+    def close(self):
+        if getattr(self, "_p", None):
+            abi.lib().ahpc_pool_destroy(self._p)
+            self._p = None
+
+    __del__ = close
+
+    @property
+    def handle(self):
+        return self._p
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def seq_create(self) -> int:
+        s = C.c_int32()
+        abi.check(abi.lib().ahpc_pool_seq_create(self._p, C.byref(s)))
+        return s.value
+
+    def seq_destroy(self, seq: int):
+        abi.check(abi.lib().ahpc_pool_seq_destroy(self._p, seq, self._stream()))
+
+    def seq_truncate(self, seq: int, new_len: int):
+        abi.check(abi.lib().ahpc_pool_seq_truncate(self._p, seq, new_len, self._stream()))
+
+    def seq_fork(self, src: int, n_prefix: int) -> int:
+        s = C.c_int32()
+        abi.check(abi.lib().ahpc_pool_seq_fork(self._p, src, n_prefix, C.byref(s), self._stream()))
+        return s.value
+
+    def append(self, seqs, n_tokens, k: torch.Tensor, v: torch.Tensor):
+        """k, v: [sum(n_tokens), heads, head_dim], the listed sequences' new tokens concatenated."""
+        seqs, n_tokens = _i32(seqs), _i32(n_tokens)
+        assert seqs.size == n_tokens.size
+        assert k.is_contiguous() and v.is_contiguous() and k.dtype == v.dtype
+        assert tuple(k.shape) == (int(n_tokens.sum()), self.heads, self.head_dim) == tuple(v.shape)
+        abi.check(abi.lib().ahpc_pool_append(self._p, _pi32(seqs), _pi32(n_tokens), seqs.size, k.data_ptr(), v.data_ptr(),
+                                             _dtype_code(k), self._stream()))
+
+    def gather(self, seq: int, start: int, n: int, dtype=None, device=None):
+        dtype = dtype or self.dtype
+        device = device if device is not None else f"cuda:{self.device}"
+        k = torch.empty((n, self.heads, self.head_dim), dtype=dtype, device=device)
+        v = torch.empty_like(k)
+        abi.check(abi.lib().ahpc_pool_gather(self._p, seq, start, n, k.data_ptr(), v.data_ptr(), _DTYPE[dtype], self._stream()))
+        return k, v
+
+    def seq_len(self, seq: int) -> int:
+        return abi.lib().ahpc_pool_seq_len(self._p, seq)
+
+    def seq_pages(self, seq: int) -> int:
+        return abi.lib().ahpc_pool_seq_pages(self._p, seq)
+
+    def free_pages_lower_bound(self) -> int:
+        return abi.lib().ahpc_pool_free_pages(self._p)
+
+    def page_bytes(self) -> int:
+        return abi.lib().ahpc_pool_page_bytes(self._p)
+
+    def live_seqs(self) -> int:
+        return abi.lib().ahpc_pool_live_seqs(self._p)
+
+    def block_table(self, seq: int, n: int | None = None) -> np.ndarray:
+        n = self.max_pages_per_seq if n is None else n
+        out = np.empty(n, dtype=np.int32)
+        abi.check(abi.lib().ahpc_pool_read_block_table(self._p, seq, _pi32(out), n, self._stream()))
+        return out
+
+    def seq_lens(self) -> np.ndarray:
+        out = np.empty(self.max_seqs, dtype=np.int32)
+        abi.check(abi.lib().ahpc_pool_read_seq_lens(self._p, _pi32(out), self.max_seqs, self._stream()))
+        return out
+
+    def refcounts(self) -> np.ndarray:
+        out = np.empty(self.num_pages, dtype=np.int32)
+        abi.check(abi.lib().ahpc_pool_read_refcounts(self._p, _pi32(out), self.num_pages, self._stream()))
+        return out
+
+    def free_ring(self) -> np.ndarray:
+        out = np.empty(self.num_pages, dtype=np.int32)
+        cnt = C.c_int64()
+        abi.check(abi.lib().ahpc_pool_read_free_ring(self._p, _pi32(out), self.num_pages, C.byref(cnt), self._stream()))
+        return out[: cnt.value].copy()
+
+    def error_flag(self) -> int:
+        f = C.c_int32()
+        abi.check(abi.lib().ahpc_pool_read_error_flag(self._p, C.byref(f), self._stream()))
+        return f.value
+
+    def decode(self, seqs, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, split_tokens=0):
+        """q: [n_seqs, heads, head_dim]; returns out of the same shape and dtype."""
+        seqs = _i32(seqs)
+        assert q.is_contiguous() and tuple(q.shape) == (seqs.size, self.heads, self.head_dim)
+        if out is None:
+            out = torch.empty_like(q)
+        assert out.is_contiguous() and out.shape == q.shape and out.dtype == q.dtype
+        a = abi.DecodeArgs()
+        a.pool, a.seqs, a.n_seqs = self._p, _pi32(seqs), seqs.size
+        a.q, a.out, a.qo_dtype = q.data_ptr(), out.data_ptr(), _dtype_code(q)
+        a.scale, a.split_tokens, a.stream = float(scale), int(split_tokens), self._stream()
+        abi.check(abi.lib().ahpc_paged_decode(C.byref(a)))
+        return out

@@ -1,0 +1,249 @@
+/*
+ * ahpc.h - C ABI of the B200 (sm_100a) attention library: FlashAttention forward and
+ * PagedAttention decode over a device-resident paged KV pool.
+ *
+ * This is the drop-in boundary.  It is shaped after the only C-level kernel interface the
+ * reference project declares, the `extern "C" launch_*_kernel(..., cudaStream_t)` launchers of
+ * src/backends/cuda/cuda_flash_attention.hpp:41-68 (declared there, never defined), and after
+ * the kernel signatures of src/backends/cuda/cuda_kernels.cu.  Everything is plain C: pointers,
+ * sizes, integers.  No exception crosses this boundary.
+ *
+ * Conventions
+ *   - Every function returns ahpc_status, whose values equal attention_hpc::AttentionError
+ *     (src/api/attention_interface.hpp:74-83); 0 is success.  A human-readable reason for the
+ *     calling thread's last failure is available from ahpc_last_error_string().
+ *   - dtype codes equal attention_hpc::DataType (attention_interface.hpp:16-20):
+ *     0 = FLOAT32, 1 = FLOAT16, 2 = BFLOAT16.  16-bit types are raw uint16 payloads
+ *     (src/api/tensor.hpp:39-41,54-56).
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Tensor pointers may be device or host pointers.  Device pointers: the call only enqueues
+ *     work on `stream` and returns.  Host pointers (what the reference's tests and examples
+ *     pass): the call stages host->device, runs, copies the result back and synchronises
+ *     `stream` before returning.
+ *   - There is no CPU execution path: without a usable sm_100 device every compute entry point
+ *     fails with BACKEND_NOT_AVAILABLE.
+ */
+#ifndef AHPC_H_
+#define AHPC_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define AHPC_API __attribute__((visibility("default")))
+#else
+#define AHPC_API
+#endif
+
+typedef int32_t ahpc_status;
+enum {
+    AHPC_SUCCESS = 0,
+    AHPC_INVALID_INPUT = 1,
+    AHPC_INVALID_PARAMETERS = 2,
+    AHPC_MEMORY_ALLOCATION_FAILED = 3,
+    AHPC_COMPUTATION_FAILED = 4,
+    AHPC_BACKEND_NOT_AVAILABLE = 5,
+    AHPC_UNSUPPORTED_OPERATION = 6,
+    AHPC_INTERNAL_ERROR = 7
+};
+
+enum { AHPC_F32 = 0, AHPC_F16 = 1, AHPC_BF16 = 2 };
+
+/* Which memory order a {B,S,H,D} dims vector describes.  The reference declares shapes
+ * {B,S,H,D} but every one of its implementations and its tests' checker index the buffer
+ * as [B,H,S,D]-contiguous (tests/test_flash_attention.cpp:46, src/algorithms/flash_attention.cpp:395,
+ * cuda_kernels.cu:150); AHPC_LAYOUT_BHSD is therefore the default of the C++ surface.
+ * AHPC_LAYOUT_BSHD is the literal reading of the dims vector. */
+enum { AHPC_LAYOUT_BHSD = 0, AHPC_LAYOUT_BSHD = 1 };
+
+/* Kernel selection for ahpc_fa_fwd. */
+enum {
+    AHPC_FA_KERNEL_AUTO = 0,   /* tensor-core kernel when the shape allows, else SIMT */
+    AHPC_FA_KERNEL_SIMT = 1,   /* FP32-FMA kernel (all dtypes, masks, any head_dim % 4 == 0 up to 256) */
+    AHPC_FA_KERNEL_TC = 2      /* tcgen05/TMEM kernel (FP16/BF16, head_dim 64 or 128, no explicit mask) */
+};
+
+/* ------------------------------------------------------------------------------------------
+ * Library
+ * ---------------------------------------------------------------------------------------- */
+
+/* "major.minor.patch" of this library. */
+AHPC_API const char* ahpc_version(void);
+
+/* Reason for the last non-zero status returned on the calling thread ("" if none). */
+AHPC_API const char* ahpc_last_error_string(void);
+
+/* Number of CUDA devices this library can run on (compute capability 10.x); 0 if none.
+ * Replaces BackendFactory::checkCudaAvailability (src/api/backend_factory.cpp:161-203). */
+AHPC_API int32_t ahpc_device_count(void);
+
+/* Properties of one device, for BackendCapability (src/api/backend_factory.hpp:24-37). */
+typedef struct ahpc_device_info {
+    char name[256];
+    uint64_t total_memory_bytes;
+    int32_t cc_major, cc_minor;
+    int32_t sm_count;
+    int32_t max_threads_per_block;
+    uint64_t max_shared_memory_per_block;
+    int32_t driver_version, runtime_version;
+} ahpc_device_info;
+AHPC_API ahpc_status ahpc_get_device_info(int32_t device, ahpc_device_info* out);
+
+/* ------------------------------------------------------------------------------------------
+ * FlashAttention forward
+ * Replaces launch_flash_attention_kernel (cuda_flash_attention.hpp:42-48), i.e. the body of
+ * FlashAttention::forward / compute_multihead_attention (src/algorithms/flash_attention.cpp:68-112,
+ * 379-450): out = softmax(scale * Q K^T + masks) V per (batch, head).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct ahpc_fa_args {
+    const void* q;            /* [batch, heads, seq_q , head_dim] through q_strides  */
+    const void* k;            /* [batch, heads, seq_kv, head_dim] through k_strides  */
+    const void* v;            /* [batch, heads, seq_kv, head_dim] through v_strides  */
+    void* out;                /* [batch, heads, seq_q , head_dim] through o_strides  */
+    const float* mask;        /* optional float [batch, seq_q, seq_kv], 0 = masked
+                                 (flash_attention.cpp:596-607); NULL = none          */
+    float* lse;               /* optional device float [batch, heads, seq_q]: natural-log
+                                 sum-exp of each row (-inf for a fully masked row)     */
+    int32_t dtype;            /* element type of q, k, v, out                        */
+    int32_t batch, heads, seq_q, seq_kv, head_dim;
+    int64_t q_strides[4];     /* element strides for (batch, head, position, dim)    */
+    int64_t k_strides[4];
+    int64_t v_strides[4];
+    int64_t o_strides[4];
+    float scale;              /* 0 = 1/sqrt(head_dim) (attention_interface.hpp:64)   */
+    int32_t causal;           /* query i sees keys 0..i (tests/test_flash_attention.cpp:56) */
+    int32_t kernel;           /* AHPC_FA_KERNEL_*                                    */
+    int32_t device;           /* CUDA device ordinal                                 */
+    void* stream;
+} ahpc_fa_args;
+
+/* Fills strides[4] for a tensor of dims {B,S,H,D} stored in `layout`. */
+AHPC_API ahpc_status ahpc_fa_strides(int32_t layout, int64_t batch, int64_t heads, int64_t seq,
+                                     int64_t head_dim, int64_t strides[4]);
+
+AHPC_API ahpc_status ahpc_fa_fwd(const ahpc_fa_args* args);
+
+/* Device bytes the library stages internally when ahpc_fa_fwd is given host pointers
+ * (FlashAttention::get_workspace_size, flash_attention.cpp:176-198). */
+AHPC_API size_t ahpc_fa_workspace_bytes(int32_t dtype, int64_t batch, int64_t heads, int64_t seq_q,
+                                        int64_t seq_kv, int64_t head_dim, int32_t with_mask);
+
+/* Which kernel ahpc_fa_fwd would run for these arguments (AHPC_FA_KERNEL_SIMT or _TC);
+ * a negative value means the arguments are invalid. */
+AHPC_API int32_t ahpc_fa_select_kernel(const ahpc_fa_args* args);
+
+/* ------------------------------------------------------------------------------------------
+ * Paged KV pool: device-resident page allocator + block table
+ * Replaces PagePool / SequenceState / KVPage (src/algorithms/paged_attention.hpp:19-122,
+ * paged_attention.cpp:11-64) and the page_table / sequence_lengths arrays the reference CUDA
+ * kernels take (cuda_kernels.cu:370-382).  Free pages form a FIFO ring in HBM; per-page
+ * reference counts allow prefix sharing; the block table int32 [max_seqs, max_pages_per_seq]
+ * and the sequence lengths live in HBM and are only ever written by kernels.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct ahpc_pool ahpc_pool;
+
+typedef struct ahpc_pool_config {
+    int32_t device;
+    int32_t dtype;               /* storage type of the pool (AHPC_F32 / F16 / BF16)             */
+    int32_t num_pages;           /* capacity, fixed at creation                                   */
+    int32_t page_size;           /* tokens per page (AttentionParams::page_size, default 16)      */
+    int32_t heads;               /* heads held by this pool (a head shard on multi-GPU runs)      */
+    int32_t head_dim;
+    int32_t max_seqs;            /* rows of the block table                                       */
+    int32_t max_pages_per_seq;   /* columns of the block table                                    */
+    const int32_t* free_order;   /* optional host int32[num_pages]: initial order of the free
+                                    ring (a permutation of 0..num_pages-1); NULL = 0,1,2,...     */
+} ahpc_pool_config;
+
+AHPC_API ahpc_status ahpc_pool_create(ahpc_pool** out, const ahpc_pool_config* config);
+AHPC_API ahpc_status ahpc_pool_destroy(ahpc_pool* pool);
+
+/* Sequence slots (rows of the block table).  create returns the lowest free slot. */
+AHPC_API ahpc_status ahpc_pool_seq_create(ahpc_pool* pool, int32_t* seq_out);
+/* Returns the sequence's pages to the ring front-to-back (paged_attention.cpp:358-363). */
+AHPC_API ahpc_status ahpc_pool_seq_destroy(ahpc_pool* pool, int32_t seq, void* stream);
+/* Drops tokens beyond new_len, releasing whole pages from the back (paged_attention.cpp:397-418). */
+AHPC_API ahpc_status ahpc_pool_seq_truncate(ahpc_pool* pool, int32_t seq, int32_t new_len, void* stream);
+/* New sequence that shares the first floor(n_prefix/page_size) pages of `src` (reference counts
+ * incremented) and owns a copy of the remaining n_prefix % page_size tokens.  No counterpart in
+ * the reference beyond shared_ptr<KVPage> (paged_attention.hpp:66). */
+AHPC_API ahpc_status ahpc_pool_seq_fork(ahpc_pool* pool, int32_t src, int32_t n_prefix,
+                                        int32_t* seq_out, void* stream);
+
+/* Appends n_tokens[i] tokens to sequence seqs[i], i < n_seqs: pages are taken from the ring in
+ * call order (deterministic), then K/V are scattered into them.  k, v: the tokens of all listed
+ * sequences concatenated, [sum(n_tokens), heads, head_dim] in kv_dtype (converted to the pool's
+ * storage type with round-to-nearest-even).  Replaces PagedAttention::append_kv_cache
+ * (paged_attention.cpp:434-462) and update_kv_cache_kernel (cuda_kernels.cu:518-563).
+ * Fails with MEMORY_ALLOCATION_FAILED, changing nothing, if pages or table columns run out. */
+AHPC_API ahpc_status ahpc_pool_append(ahpc_pool* pool, const int32_t* seqs, const int32_t* n_tokens,
+                                      int32_t n_seqs, const void* k, const void* v, int32_t kv_dtype,
+                                      void* stream);
+
+/* Copies tokens [start, start+n) of a sequence out of the pool as [n, heads, head_dim] in
+ * out_dtype.  Replaces PagedAttention::get_kv_cache (paged_attention.cpp:464-490). */
+AHPC_API ahpc_status ahpc_pool_gather(ahpc_pool* pool, int32_t seq, int32_t start, int32_t n,
+                                      void* k_out, void* v_out, int32_t out_dtype, void* stream);
+
+/* Host-side mirrors kept by the library (no device access). */
+AHPC_API int32_t ahpc_pool_seq_len(const ahpc_pool* pool, int32_t seq);       /* -1 if not live */
+AHPC_API int32_t ahpc_pool_seq_pages(const ahpc_pool* pool, int32_t seq);
+AHPC_API int64_t ahpc_pool_free_pages(const ahpc_pool* pool);
+AHPC_API int64_t ahpc_pool_page_bytes(const ahpc_pool* pool);                 /* K + V of one page */
+AHPC_API int32_t ahpc_pool_live_seqs(const ahpc_pool* pool);
+
+/* Device state read back (synchronises `stream`); for bit-exact checks against a CPU model. */
+AHPC_API ahpc_status ahpc_pool_read_block_table(ahpc_pool* pool, int32_t seq, int32_t* out, int32_t n,
+                                                void* stream);
+AHPC_API ahpc_status ahpc_pool_read_seq_lens(ahpc_pool* pool, int32_t* out, int32_t n, void* stream);
+AHPC_API ahpc_status ahpc_pool_read_refcounts(ahpc_pool* pool, int32_t* out, int32_t n, void* stream);
+/* Order of the free ring, front first; *count_out receives the number of free pages. */
+AHPC_API ahpc_status ahpc_pool_read_free_ring(ahpc_pool* pool, int32_t* out, int32_t n,
+                                              int64_t* count_out, void* stream);
+/* Non-zero if any allocator kernel met an inconsistency (ring underflow, bad page id). */
+AHPC_API ahpc_status ahpc_pool_read_error_flag(ahpc_pool* pool, int32_t* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * PagedAttention decode
+ * Replaces PagedAttention::forward_batch / compute_paged_attention (paged_attention.cpp:496-547,
+ * 596-680) and paged_attention_kernel (cuda_kernels.cu:370-515) for one query token per
+ * sequence: out[i,h,:] = softmax(scale * q[i,h,:] . K_seq^T) V_seq over all tokens of seqs[i].
+ * ---------------------------------------------------------------------------------------- */
+typedef struct ahpc_decode_args {
+    ahpc_pool* pool;
+    const int32_t* seqs;      /* host int32[n_seqs]: sequence slots, duplicates allowed     */
+    int32_t n_seqs;
+    const void* q;            /* [n_seqs, heads, head_dim] in qo_dtype, contiguous          */
+    void* out;                /* [n_seqs, heads, head_dim] in qo_dtype, contiguous          */
+    int32_t qo_dtype;
+    float scale;              /* 0 = 1/sqrt(head_dim) (paged_attention.cpp:634)             */
+    int32_t split_tokens;     /* tokens per split-KV chunk; 0 = library default; must be a
+                                 multiple of the page size                                  */
+    void* stream;
+} ahpc_decode_args;
+
+AHPC_API ahpc_status ahpc_paged_decode(const ahpc_decode_args* args);
+
+/* Bytes of split-KV scratch (partial outputs and log-sum-exp) a decode of n_seqs sequences of
+ * at most max_len tokens needs; the library keeps this buffer per pool and grows it on demand. */
+AHPC_API size_t ahpc_paged_decode_scratch_bytes(const ahpc_pool* pool, int32_t n_seqs, int32_t max_len,
+                                                int32_t split_tokens);
+
+/* ------------------------------------------------------------------------------------------
+ * Multi-GPU partitioning (host arithmetic only; no communication)
+ * The (batch, head) pairs of a FlashAttention call, or the heads of a decode pool, are split
+ * into `world` contiguous ranges, the first (units % world) ranges one unit longer.  The
+ * reference only declares this (cuda_flash_attention_utils::distribute_workload,
+ * cuda_flash_attention.hpp:430-432).
+ * ---------------------------------------------------------------------------------------- */
+AHPC_API ahpc_status ahpc_shard_range(int64_t units, int32_t world, int32_t rank,
+                                      int64_t* begin_out, int64_t* end_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AHPC_H_ */

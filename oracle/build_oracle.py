@@ -1,0 +1,78 @@
+"""Build recipes for the CPU oracle (test infrastructure, never part of the product library).
+
+  build_oracle()           oracle/oracle.c  -> oracle/_build/liboracle.so   (portable x86-64, OpenMP)
+  build_oracle(native=True)                 -> oracle/_build/liboracle_native.so (-march=native, for
+                                               timing the CPU baseline on the machine it runs on)
+  build_ref(reference_root) compiles the reference project's own checker
+                           (tests/test_flash_attention.cpp:30-97 and :523-578) from where it lies
+                           into oracle/_ref/libref_attention.so.  Only line ranges are streamed to
+                           the compiler through file descriptors; no reference text is written
+                           into this repository.
+
+Run as a script to build everything that can be built on this machine.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+BUILD_DIR = os.path.join(HERE, "_build")
+REF_DIR = os.path.join(HERE, "_ref")
+REF_TEST_FILE = "tests/test_flash_attention.cpp"
+REF_FN_LINES = (30, 97)
+REF_MASK_LINES = (523, 578)
+
+
+def _newer(target: str, *sources: str) -> bool:
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def build_oracle(native: bool = False, force: bool = False) -> str:
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    src = os.path.join(HERE, "oracle.c")
+    out = os.path.join(BUILD_DIR, "liboracle_native.so" if native else "liboracle.so")
+    if not force and _newer(out, src):
+        return out
+    cmd = ["gcc", "-O3", "-std=c11", "-fPIC", "-shared", "-fopenmp", "-fvisibility=hidden",
+           "-fno-math-errno", src, "-o", out, "-lm"]
+    if native:
+        cmd.insert(2, "-march=native")
+    subprocess.run(cmd, check=True)
+    return out
+
+
+def ref_lib_path() -> str:
+    return os.path.join(REF_DIR, "libref_attention.so")
+
+
+def build_ref(reference_root: str = "/root/reference", force: bool = False) -> str | None:
+    """Returns the path of the built library, or None when the reference tree is not present."""
+    test_file = os.path.join(reference_root, REF_TEST_FILE)
+    out = ref_lib_path()
+    shim = os.path.join(HERE, "ref_shim.cpp")
+    if not os.path.exists(test_file):
+        return out if os.path.exists(out) else None
+    if not force and _newer(out, shim, test_file):
+        return out
+    os.makedirs(REF_DIR, exist_ok=True)
+    script = (
+        "set -e; exec g++ -O2 -std=c++17 -fPIC -shared -fvisibility=hidden "
+        "-DREF_FN_SRC='\"/dev/fd/3\"' -DREF_MASK_SRC='\"/dev/fd/4\"' "
+        f"'{shim}' -o '{out}' "
+        f"3< <(sed -n '{REF_FN_LINES[0]},{REF_FN_LINES[1]}p' '{test_file}') "
+        f"4< <(sed -n '{REF_MASK_LINES[0]},{REF_MASK_LINES[1]}p' '{test_file}')"
+    )
+    subprocess.run(["bash", "-c", script], check=True)
+    return out
+
+
+if __name__ == "__main__":
+    print(build_oracle())
+    print(build_ref() or "reference tree absent: oracle/_ref not rebuilt")
+    if "--native" in sys.argv:
+        print(build_oracle(native=True))

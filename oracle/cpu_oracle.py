@@ -1,0 +1,233 @@
+"""numpy-facing wrapper around the CPU oracle (oracle/oracle.c) and, when present, the
+reference project's own checker (oracle/_ref).  TEST INFRASTRUCTURE ONLY: imported by tests/,
+by the smoke check and by the CPU-baseline leg of the benchmark, never by the product package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import build_oracle as _b
+
+_F = C.POINTER(C.c_float)
+_I32 = C.POINTER(C.c_int32)
+_I64 = C.POINTER(C.c_int64)
+_LIBS: dict[str, C.CDLL] = {}
+
+DTYPE_CODE = {"f32": 0, "f16": 1, "bf16": 2}
+
+
+def _lib(native: bool = False) -> C.CDLL:
+    key = "native" if native else "portable"
+    if key not in _LIBS:
+        lib = C.CDLL(_b.build_oracle(native=native))
+        lib.oracle_attention_fwd.argtypes = [_F, _F, _F, _F, _F] + [C.c_int64] * 5 + [_I64] * 4 + [C.c_float, C.c_int, _F]
+        lib.oracle_attention_fwd_f32acc.argtypes = [_F, _F, _F, _F] + [C.c_int64] * 4 + [C.c_float, C.c_int, C.c_int]
+        lib.oracle_paged_decode.argtypes = [_F, _F, _F, _F, _I32, _I32] + [C.c_int64] * 5 + [C.c_float]
+        lib.oracle_paged_decode_f32acc.argtypes = [_F, C.c_void_p, C.c_void_p, _F, _I32, _I32] + [C.c_int64] * 5 + [C.c_float, C.c_int, C.c_int]
+        lib.oracle_convert_to_f32.argtypes = [C.c_void_p, _F, C.c_int64, C.c_int]
+        lib.oracle_convert_from_f32.argtypes = [_F, C.c_void_p, C.c_int64, C.c_int]
+        lib.oracle_pool_create.restype = C.c_void_p
+        lib.oracle_pool_create.argtypes = [C.c_int32] * 4 + [_I32]
+        lib.oracle_pool_destroy.argtypes = [C.c_void_p]
+        lib.oracle_pool_seq_create.argtypes = [C.c_void_p]
+        lib.oracle_pool_append.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
+        lib.oracle_pool_truncate.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
+        lib.oracle_pool_seq_destroy.argtypes = [C.c_void_p, C.c_int32]
+        lib.oracle_pool_fork.argtypes = [C.c_void_p, C.c_int32, C.c_int32, _I32, _I32]
+        lib.oracle_pool_seq_len.argtypes = [C.c_void_p, C.c_int32]
+        lib.oracle_pool_seq_pages.argtypes = [C.c_void_p, C.c_int32]
+        lib.oracle_pool_free_count.argtypes = [C.c_void_p]
+        lib.oracle_pool_free_count.restype = C.c_int64
+        lib.oracle_pool_refcount.argtypes = [C.c_void_p, C.c_int32]
+        lib.oracle_pool_block_table.argtypes = [C.c_void_p, C.c_int32, _I32, C.c_int32]
+        _LIBS[key] = lib
+    return _LIBS[key]
+
+
+def _fp(a: np.ndarray):
+    return a.ctypes.data_as(_F)
+
+
+# ------------------------------------------------------------------ 16-bit payloads
+
+def round_to(a: np.ndarray, dtype: str) -> np.ndarray:
+    """float32 -> payload of `dtype` (uint16 for f16/bf16) with round-to-nearest-even."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    if dtype == "f32":
+        return a.copy()
+    out = np.empty(a.shape, dtype=np.uint16)
+    _lib().oracle_convert_from_f32(_fp(a), out.ctypes.data, a.size, DTYPE_CODE[dtype])
+    return out
+
+
+def widen(a: np.ndarray, dtype: str) -> np.ndarray:
+    """payload of `dtype` -> float32 (exact)."""
+    if dtype == "f32":
+        return np.ascontiguousarray(a, dtype=np.float32)
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    out = np.empty(a.shape, dtype=np.float32)
+    _lib().oracle_convert_to_f32(a.ctypes.data, _fp(out), a.size, DTYPE_CODE[dtype])
+    return out
+
+
+# ------------------------------------------------------------------ dense attention
+
+def attention_fwd(q, k, v, scale: float, causal: bool = False, mask=None, return_lse: bool = False):
+    """q: float32 view indexed [B, H, Sq, D]; k, v: [B, H, Skv, D]; any strides.
+    Returns float32 [B, H, Sq, D] (contiguous) and optionally lse [B, H, Sq]."""
+    assert q.dtype == np.float32 and k.dtype == np.float32 and v.dtype == np.float32
+    B, H, Sq, D = q.shape
+    Skv = k.shape[2]
+    out = np.zeros((B, H, Sq, D), dtype=np.float32)
+    lse = np.zeros((B, H, Sq), dtype=np.float32) if return_lse else None
+
+    def es(a):
+        return (C.c_int64 * 4)(*[s // 4 for s in a.strides])
+
+    m = None
+    if mask is not None:
+        m = np.ascontiguousarray(mask, dtype=np.float32)
+        assert m.shape == (B, Sq, Skv)
+    _lib().oracle_attention_fwd(
+        _fp(q), _fp(k), _fp(v), _fp(out), _fp(lse) if lse is not None else None,
+        B, H, Sq, Skv, D, es(q), es(k), es(v), es(out), float(scale), int(causal),
+        _fp(m) if m is not None else None)
+    return (out, lse) if return_lse else out
+
+
+def attention_fwd_f32acc(q, k, v, scale: float, causal: bool, threads: int = 0, native: bool = False):
+    """The float-accumulating port (contiguous [B,H,S,D]); this is what the CPU baseline times."""
+    q, k, v = (np.ascontiguousarray(x, dtype=np.float32) for x in (q, k, v))
+    B, H, S, D = q.shape
+    out = np.empty_like(q)
+    _lib(native).oracle_attention_fwd_f32acc(_fp(q), _fp(k), _fp(v), _fp(out), B, H, S, D,
+                                             float(scale), int(causal), int(threads))
+    return out
+
+
+# ------------------------------------------------------------------ paged decode
+
+def paged_decode(q, k_cache, v_cache, page_table, seq_lens, scale: float):
+    """q [n, H, D]; caches [num_pages, page_size, H, D]; page_table int32 [n, max_pages]."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k_cache = np.ascontiguousarray(k_cache, dtype=np.float32)
+    v_cache = np.ascontiguousarray(v_cache, dtype=np.float32)
+    pt = np.ascontiguousarray(page_table, dtype=np.int32)
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    n, H, D = q.shape
+    out = np.zeros_like(q)
+    _lib().oracle_paged_decode(_fp(q), _fp(k_cache), _fp(v_cache), _fp(out),
+                               pt.ctypes.data_as(_I32), sl.ctypes.data_as(_I32),
+                               n, H, D, k_cache.shape[1], pt.shape[1], float(scale))
+    return out
+
+
+def paged_decode_f32acc(q, k_cache, v_cache, dtype: str, page_table, seq_lens, scale: float,
+                        threads: int = 0, native: bool = False):
+    """Float-accumulating port over a pool stored in `dtype` payloads; timed as the CPU baseline."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    pt = np.ascontiguousarray(page_table, dtype=np.int32)
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    assert k_cache.flags.c_contiguous and v_cache.flags.c_contiguous
+    n, H, D = q.shape
+    out = np.zeros_like(q)
+    _lib(native).oracle_paged_decode_f32acc(_fp(q), k_cache.ctypes.data, v_cache.ctypes.data, _fp(out),
+                                            pt.ctypes.data_as(_I32), sl.ctypes.data_as(_I32),
+                                            n, H, D, k_cache.shape[1], pt.shape[1], float(scale),
+                                            DTYPE_CODE[dtype], int(threads))
+    return out
+
+
+# ------------------------------------------------------------------ allocator model
+
+class PoolModel:
+    """FIFO page allocator with reference counts; the block-table oracle."""
+
+    def __init__(self, num_pages, page_size, max_seqs, max_pages, free_order=None):
+        self._lib = _lib()
+        fo = None
+        if free_order is not None:
+            fo = np.ascontiguousarray(free_order, dtype=np.int32)
+            assert fo.shape == (num_pages,)
+        self._p = self._lib.oracle_pool_create(num_pages, page_size, max_seqs, max_pages,
+                                               fo.ctypes.data_as(_I32) if fo is not None else None)
+        self.num_pages, self.page_size, self.max_seqs, self.max_pages = num_pages, page_size, max_seqs, max_pages
+
+    def __del__(self):
+        if getattr(self, "_p", None):
+            self._lib.oracle_pool_destroy(self._p)
+            self._p = None
+
+    def seq_create(self) -> int:
+        return self._lib.oracle_pool_seq_create(self._p)
+
+    def append(self, seq: int, n_tokens: int) -> int:
+        return self._lib.oracle_pool_append(self._p, seq, n_tokens)
+
+    def truncate(self, seq: int, new_len: int) -> None:
+        self._lib.oracle_pool_truncate(self._p, seq, new_len)
+
+    def seq_destroy(self, seq: int) -> None:
+        self._lib.oracle_pool_seq_destroy(self._p, seq)
+
+    def fork(self, src: int, n_prefix: int):
+        a, b = C.c_int32(-1), C.c_int32(-1)
+        dst = self._lib.oracle_pool_fork(self._p, src, n_prefix, C.byref(a), C.byref(b))
+        return dst, a.value, b.value
+
+    def seq_len(self, seq: int) -> int:
+        return self._lib.oracle_pool_seq_len(self._p, seq)
+
+    def seq_pages(self, seq: int) -> int:
+        return self._lib.oracle_pool_seq_pages(self._p, seq)
+
+    def free_count(self) -> int:
+        return self._lib.oracle_pool_free_count(self._p)
+
+    def refcount(self, page: int) -> int:
+        return self._lib.oracle_pool_refcount(self._p, page)
+
+    def block_table(self, seq: int, n: int | None = None) -> np.ndarray:
+        n = self.max_pages if n is None else n
+        out = np.empty(n, dtype=np.int32)
+        self._lib.oracle_pool_block_table(self._p, seq, out.ctypes.data_as(_I32), n)
+        return out
+
+
+# ------------------------------------------------------------------ the reference's own checker
+
+def ref_available() -> bool:
+    return os.path.exists(_b.ref_lib_path()) or _b.build_ref() is not None
+
+
+def _ref():
+    if "ref" not in _LIBS:
+        path = _b.build_ref()
+        if path is None:
+            raise RuntimeError("oracle/_ref is not built and the reference tree is absent")
+        lib = C.CDLL(path)
+        lib.ref_compute_reference_attention.argtypes = [_F, _F, _F, _F] + [C.c_size_t] * 4 + [C.c_float, C.c_int]
+        lib.ref_masked_reference_attention.argtypes = [_F, _F, _F, _F, _F] + [C.c_size_t] * 4 + [C.c_float]
+        _LIBS["ref"] = lib
+    return _LIBS["ref"]
+
+
+def ref_attention(q, k, v, scale: float, causal: bool) -> np.ndarray:
+    """The reference's compute_reference_attention on contiguous [B,H,S,D] float32 buffers."""
+    q, k, v = (np.ascontiguousarray(x, dtype=np.float32) for x in (q, k, v))
+    B, H, S, D = q.shape
+    out = np.empty_like(q)
+    _ref().ref_compute_reference_attention(_fp(q), _fp(k), _fp(v), _fp(out), B, H, S, D, float(scale), int(causal))
+    return out
+
+
+def ref_masked_attention(q, k, v, mask, scale: float) -> np.ndarray:
+    q, k, v = (np.ascontiguousarray(x, dtype=np.float32) for x in (q, k, v))
+    mask = np.ascontiguousarray(mask, dtype=np.float32)
+    B, H, S, D = q.shape
+    out = np.empty_like(q)
+    _ref().ref_masked_reference_attention(_fp(q), _fp(k), _fp(v), _fp(mask), _fp(out), B, H, S, D, float(scale))
+    return out

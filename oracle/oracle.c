@@ -1,0 +1,440 @@
+/*
+ * CPU oracle for the two attention hot paths.  TEST INFRASTRUCTURE ONLY: nothing in the
+ * product library links, loads or calls this file; it exists so that the CUDA kernels can
+ * be checked against a slow, obviously-correct restatement of the reference semantics.
+ *
+ * What it restates (paths are inside the reference project):
+ *   - dense attention: tests/test_flash_attention.cpp:30-97 (compute_reference_attention:
+ *     scores = q.k * scale, causal "q_idx < k_idx => -inf" at :56-58, row softmax with max
+ *     subtraction :73-84, O = W.V :87-93) and the [B,S,S] float mask variant at :519-578
+ *     ("mask == 0 => -inf", :537).  Buffer indexing (b*H+h)*S*D + s*D + d (:46) is the
+ *     default; strides are explicit so the declared {B,S,H,D} order can be exercised too.
+ *   - the online-softmax merge the reference intends: src/algorithms/flash_attention.hpp:39-62
+ *     (OnlineSoftmaxState::update / get_normalizer: a row whose weights sum to 0 gets
+ *     normaliser 0, i.e. an all-masked row yields zeros, not NaN).
+ *   - paged decode: src/backends/cuda/cuda_kernels.cu:370-515 (page_table int32
+ *     [batch, max_pages_per_sequence], entries < 0 terminate the walk :419-420,
+ *     sequence_lengths int32 [batch], K/V cache [num_pages, page_size, H, D] :439-440,
+ *     query/output [batch, H, D], scale 1/sqrt(D) src/algorithms/paged_attention.cpp:634);
+ *     decode = the single query attends to all seq_len keys.
+ *   - page allocator: src/algorithms/paged_attention.cpp:16-64 (PagePool: FIFO free queue,
+ *     pop front :23-24, push back :37), :333-432 (sequence page lists,
+ *     pages needed = ceil(len / page_size)).
+ *   - 16-bit storage: src/api/tensor.hpp:39-66 declares half/bfloat16 as uint16 payloads with
+ *     conversions left undefined; round-to-nearest-even is used here.
+ *
+ * Parity status: the dense path is pinned against the reference's own
+ * compute_reference_attention compiled from where it lies (oracle/_ref, see
+ * oracle/build_oracle.py) and against fixtures generated with it (tests/golden).  The
+ * paged path is "parity unpinned": the reference has no test, fixture or complete
+ * implementation for it; it is pinned here only by the property that paged decode equals
+ * dense attention on the gathered K/V.
+ *
+ * All accumulation is in double.  `*_f32acc` variants accumulate in float with the
+ * reference loop nest; they are the "port" that the CPU baseline times.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORACLE_API __attribute__((visibility("default")))
+
+/* ---------------------------------------------------------------- 16-bit conversions */
+
+ORACLE_API uint16_t oracle_f32_to_bf16(float f) {
+    uint32_t u; memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u); /* quiet NaN */
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;                       /* round to nearest, ties to even */
+    return (uint16_t)(u >> 16);
+}
+
+ORACLE_API float oracle_bf16_to_f32(uint16_t h) {
+    uint32_t u = ((uint32_t)h) << 16; float f; memcpy(&f, &u, 4); return f;
+}
+
+ORACLE_API float oracle_f16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu, man = h & 0x3ffu, u;
+    if (exp == 0) {
+        if (man == 0) u = sign;
+        else {                                 /* subnormal: renormalise */
+            int e = -1; do { e++; man <<= 1; } while (!(man & 0x400u));
+            u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) u = sign | 0x7f800000u | (man << 13);
+    else u = sign | ((exp + 112u) << 23) | (man << 13);
+    float f; memcpy(&f, &u, 4); return f;
+}
+
+ORACLE_API uint16_t oracle_f32_to_f16(float f) {
+    uint32_t u; memcpy(&u, &f, 4);
+    uint32_t sign = (u >> 16) & 0x8000u; u &= 0x7fffffffu;
+    if (u > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);
+    if (u >= 0x47800000u) return (uint16_t)(sign | 0x7c00u);           /* >= 65536 -> inf */
+    if (u < 0x33000000u) return (uint16_t)sign;                         /* < 2^-25 -> 0 */
+    if (u < 0x38800000u) {                                              /* subnormal result */
+        int shift = 126 - (int)(u >> 23);                               /* 14..24 */
+        uint32_t man = (u & 0x7fffffu) | 0x800000u;
+        uint32_t half = man >> shift, rem = man & ((1u << shift) - 1u), mid = 1u << (shift - 1);
+        if (rem > mid || (rem == mid && (half & 1u))) half++;
+        return (uint16_t)(sign | half);
+    }
+    uint32_t half = ((u >> 13) - (112u << 10));
+    uint32_t rem = u & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (half & 1u))) half++;       /* may carry to inf */
+    return (uint16_t)(sign | half);
+}
+
+ORACLE_API void oracle_convert_to_f32(const void* src, float* dst, int64_t n, int dtype) {
+    if (dtype == 0) memcpy(dst, src, (size_t)n * 4);
+    else if (dtype == 1) for (int64_t i = 0; i < n; ++i) dst[i] = oracle_f16_to_f32(((const uint16_t*)src)[i]);
+    else for (int64_t i = 0; i < n; ++i) dst[i] = oracle_bf16_to_f32(((const uint16_t*)src)[i]);
+}
+
+ORACLE_API void oracle_convert_from_f32(const float* src, void* dst, int64_t n, int dtype) {
+    if (dtype == 0) memcpy(dst, src, (size_t)n * 4);
+    else if (dtype == 1) for (int64_t i = 0; i < n; ++i) ((uint16_t*)dst)[i] = oracle_f32_to_f16(src[i]);
+    else for (int64_t i = 0; i < n; ++i) ((uint16_t*)dst)[i] = oracle_f32_to_bf16(src[i]);
+}
+
+/* ---------------------------------------------------------------- dense attention */
+
+/*
+ * out[b,h,i,:] = softmax_j(scale * q[b,h,i,:].k[b,h,j,:] + masks) . v[b,h,j,:]
+ * Strides are in elements for (b, h, s, d).  mask may be NULL; otherwise float
+ * [B, seq_q, seq_kv] with 0 meaning "masked".  Causal masks j > i (query i sees keys 0..i).
+ * Rows with no visible key produce zeros.  lse (optional, [B,H,seq_q]) receives
+ * log(sum exp(score)) in natural log units, -inf for empty rows.
+ */
+ORACLE_API void oracle_attention_fwd(
+    const float* q, const float* k, const float* v, float* out, float* lse,
+    int64_t B, int64_t H, int64_t seq_q, int64_t seq_kv, int64_t D,
+    const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os,
+    float scale, int causal, const float* mask)
+{
+    #pragma omp parallel
+    {
+        double* score = (double*)malloc(sizeof(double) * (size_t)(seq_kv > 0 ? seq_kv : 1));
+        double* acc = (double*)malloc(sizeof(double) * (size_t)D);
+        #pragma omp for collapse(2) schedule(dynamic, 1)
+        for (int64_t bh = 0; bh < B * H; ++bh) {
+            for (int64_t i = 0; i < seq_q; ++i) {
+                int64_t b = bh / H, h = bh % H;
+                const float* qrow = q + b * qs[0] + h * qs[1] + i * qs[2];
+                double m = -INFINITY;
+                for (int64_t j = 0; j < seq_kv; ++j) {
+                    int visible = !(causal && i < j);
+                    if (visible && mask && mask[(b * seq_q + i) * seq_kv + j] == 0.0f) visible = 0;
+                    if (!visible) { score[j] = -INFINITY; continue; }
+                    const float* krow = k + b * ks[0] + h * ks[1] + j * ks[2];
+                    double dot = 0.0;
+                    for (int64_t d = 0; d < D; ++d) dot += (double)qrow[d * qs[3]] * (double)krow[d * ks[3]];
+                    score[j] = dot * (double)scale;
+                    if (score[j] > m) m = score[j];
+                }
+                double sum = 0.0;
+                for (int64_t d = 0; d < D; ++d) acc[d] = 0.0;
+                if (m > -INFINITY) {
+                    for (int64_t j = 0; j < seq_kv; ++j) {
+                        if (score[j] == -INFINITY) continue;
+                        double w = exp(score[j] - m);
+                        sum += w;
+                        const float* vrow = v + b * vs[0] + h * vs[1] + j * vs[2];
+                        for (int64_t d = 0; d < D; ++d) acc[d] += w * (double)vrow[d * vs[3]];
+                    }
+                }
+                double inv = sum > 0.0 ? 1.0 / sum : 0.0;
+                float* orow = out + b * os[0] + h * os[1] + i * os[2];
+                for (int64_t d = 0; d < D; ++d) orow[d * os[3]] = (float)(acc[d] * inv);
+                if (lse) lse[(b * H + h) * seq_q + i] = sum > 0.0 ? (float)(m + log(sum)) : -INFINITY;
+            }
+        }
+        free(score); free(acc);
+    }
+}
+
+/*
+ * The same loop nest as the reference's test helper, float accumulation, contiguous
+ * [B,H,S,D] buffers, parallel over (b,h).  This is the "port" timed as the CPU baseline.
+ */
+ORACLE_API void oracle_attention_fwd_f32acc(
+    const float* q, const float* k, const float* v, float* out,
+    int64_t B, int64_t H, int64_t S, int64_t D, float scale, int causal, int num_threads)
+{
+#ifdef _OPENMP
+    if (num_threads > 0) omp_set_num_threads(num_threads);
+#endif
+    #pragma omp parallel
+    {
+        float* w = (float*)malloc(sizeof(float) * (size_t)S);
+        #pragma omp for collapse(2) schedule(dynamic, 8)
+        for (int64_t bh = 0; bh < B * H; ++bh) {
+            for (int64_t i = 0; i < S; ++i) {
+                const float* qb = q + bh * S * D; const float* kb = k + bh * S * D;
+                const float* vb = v + bh * S * D; float* ob = out + bh * S * D;
+                int64_t n = causal ? i + 1 : S;
+                float m = -INFINITY;
+                for (int64_t j = 0; j < n; ++j) {
+                    float dot = 0.f;
+                    for (int64_t d = 0; d < D; ++d) dot += qb[i * D + d] * kb[j * D + d];
+                    w[j] = dot * scale;
+                    if (w[j] > m) m = w[j];
+                }
+                float sum = 0.f;
+                for (int64_t j = 0; j < n; ++j) { w[j] = expf(w[j] - m); sum += w[j]; }
+                float inv = 1.f / sum;
+                for (int64_t d = 0; d < D; ++d) ob[i * D + d] = 0.f;
+                for (int64_t j = 0; j < n; ++j) {
+                    float p = w[j] * inv;
+                    for (int64_t d = 0; d < D; ++d) ob[i * D + d] += p * vb[j * D + d];
+                }
+            }
+        }
+        free(w);
+    }
+}
+
+/* ---------------------------------------------------------------- paged decode */
+
+/*
+ * One query token per sequence.  q,out: [n_seqs, H, D] float.  k_cache, v_cache:
+ * [num_pages, page_size, H, D] float (the reference CUDA kernel's cache layout).
+ * page_table: int32 [n_seqs, max_pages]; entry < 0 ends the walk.  seq_lens int32 [n_seqs].
+ * A sequence of length 0 produces zeros.
+ */
+ORACLE_API void oracle_paged_decode(
+    const float* q, const float* k_cache, const float* v_cache, float* out,
+    const int32_t* page_table, const int32_t* seq_lens,
+    int64_t n_seqs, int64_t H, int64_t D, int64_t page_size, int64_t max_pages, float scale)
+{
+    #pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t s = 0; s < n_seqs; ++s) {
+        for (int64_t h = 0; h < H; ++h) {
+            int64_t len = seq_lens[s];
+            int64_t npages = (len + page_size - 1) / page_size;
+            double* score = (double*)malloc(sizeof(double) * (size_t)(len > 0 ? len : 1));
+            double* acc = (double*)calloc((size_t)D, sizeof(double));
+            const float* qrow = q + (s * H + h) * D;
+            double m = -INFINITY; int64_t seen = 0;
+            for (int64_t p = 0; p < npages; ++p) {
+                int32_t page = page_table[s * max_pages + p];
+                if (page < 0) break;
+                for (int64_t t = 0; t < page_size && p * page_size + t < len; ++t) {
+                    const float* krow = k_cache + (((int64_t)page * page_size + t) * H + h) * D;
+                    double dot = 0.0;
+                    for (int64_t d = 0; d < D; ++d) dot += (double)qrow[d] * (double)krow[d];
+                    score[seen] = dot * (double)scale;
+                    if (score[seen] > m) m = score[seen];
+                    ++seen;
+                }
+            }
+            double sum = 0.0; int64_t idx = 0;
+            for (int64_t p = 0; p < npages && idx < seen; ++p) {
+                int32_t page = page_table[s * max_pages + p];
+                if (page < 0) break;
+                for (int64_t t = 0; t < page_size && idx < seen && p * page_size + t < len; ++t, ++idx) {
+                    double w = exp(score[idx] - m);
+                    sum += w;
+                    const float* vrow = v_cache + (((int64_t)page * page_size + t) * H + h) * D;
+                    for (int64_t d = 0; d < D; ++d) acc[d] += w * (double)vrow[d];
+                }
+            }
+            double inv = sum > 0.0 ? 1.0 / sum : 0.0;
+            for (int64_t d = 0; d < D; ++d) out[(s * H + h) * D + d] = (float)(acc[d] * inv);
+            free(score); free(acc);
+        }
+    }
+}
+
+/*
+ * Float-accumulating port of the reference's CPU decode structure
+ * (src/algorithms/paged_attention.cpp:596-680: per head, gather the whole context into a
+ * contiguous buffer, dot, softmax, weighted sum), with the "mask every key but the first"
+ * defect left out.  16-bit pool payloads are widened while gathering.  Timed as the CPU
+ * baseline for the decode path; parallel over (sequence, head).
+ * k_cache/v_cache: [num_pages, page_size, H, D] in `dtype` (0 f32, 1 f16, 2 bf16).
+ */
+ORACLE_API void oracle_paged_decode_f32acc(
+    const float* q, const void* k_cache, const void* v_cache, float* out,
+    const int32_t* page_table, const int32_t* seq_lens,
+    int64_t n_seqs, int64_t H, int64_t D, int64_t page_size, int64_t max_pages, float scale,
+    int dtype, int num_threads)
+{
+#ifdef _OPENMP
+    if (num_threads > 0) omp_set_num_threads(num_threads);
+#endif
+    #pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t s = 0; s < n_seqs; ++s) {
+        for (int64_t h = 0; h < H; ++h) {
+            int64_t len = seq_lens[s];
+            float* kb = (float*)malloc(sizeof(float) * (size_t)(len * D + 1));
+            float* vb = (float*)malloc(sizeof(float) * (size_t)(len * D + 1));
+            float* w = (float*)malloc(sizeof(float) * (size_t)(len + 1));
+            for (int64_t t = 0; t < len; ++t) {           /* gather_keys_values */
+                int32_t page = page_table[s * max_pages + t / page_size];
+                int64_t off = (((int64_t)page * page_size + t % page_size) * H + h) * D;
+                if (dtype == 0) {
+                    memcpy(kb + t * D, (const float*)k_cache + off, (size_t)D * 4);
+                    memcpy(vb + t * D, (const float*)v_cache + off, (size_t)D * 4);
+                } else {
+                    const uint16_t* ks = (const uint16_t*)k_cache + off;
+                    const uint16_t* vs = (const uint16_t*)v_cache + off;
+                    for (int64_t d = 0; d < D; ++d) {
+                        kb[t * D + d] = dtype == 1 ? oracle_f16_to_f32(ks[d]) : oracle_bf16_to_f32(ks[d]);
+                        vb[t * D + d] = dtype == 1 ? oracle_f16_to_f32(vs[d]) : oracle_bf16_to_f32(vs[d]);
+                    }
+                }
+            }
+            const float* qrow = q + (s * H + h) * D;
+            float m = -INFINITY;
+            for (int64_t t = 0; t < len; ++t) {
+                float dot = 0.f;
+                for (int64_t d = 0; d < D; ++d) dot += qrow[d] * kb[t * D + d];
+                w[t] = dot * scale; if (w[t] > m) m = w[t];
+            }
+            float sum = 0.f;
+            for (int64_t t = 0; t < len; ++t) { w[t] = expf(w[t] - m); sum += w[t]; }
+            float inv = sum > 0.f ? 1.f / sum : 0.f;
+            float* orow = out + (s * H + h) * D;
+            for (int64_t d = 0; d < D; ++d) orow[d] = 0.f;
+            for (int64_t t = 0; t < len; ++t) {
+                float p = w[t] * inv;
+                for (int64_t d = 0; d < D; ++d) orow[d] += p * vb[t * D + d];
+            }
+            free(kb); free(vb); free(w);
+        }
+    }
+}
+
+/* ---------------------------------------------------------------- page allocator model */
+
+/*
+ * FIFO page pool with reference counts and per-sequence page lists (the block table).
+ * Pages leave the front of the free queue and return to its back, as the reference's
+ * std::queue does.  Reference counts let several sequences name one physical page
+ * (prefix sharing); a page returns to the queue when its count reaches zero.
+ */
+typedef struct oracle_pool {
+    int32_t num_pages, page_size, max_seqs, max_pages;
+    int32_t* ring; int64_t head, count;          /* free queue */
+    int32_t* refcount;                           /* [num_pages] */
+    int32_t* table;                              /* [max_seqs, max_pages], -1 = none */
+    int32_t* seq_len; int32_t* seq_pages; int32_t* seq_live;
+} oracle_pool;
+
+ORACLE_API oracle_pool* oracle_pool_create(int32_t num_pages, int32_t page_size, int32_t max_seqs,
+                                           int32_t max_pages, const int32_t* free_order) {
+    oracle_pool* p = (oracle_pool*)calloc(1, sizeof(oracle_pool));
+    p->num_pages = num_pages; p->page_size = page_size; p->max_seqs = max_seqs; p->max_pages = max_pages;
+    p->ring = (int32_t*)malloc(sizeof(int32_t) * (size_t)num_pages);
+    for (int32_t i = 0; i < num_pages; ++i) p->ring[i] = free_order ? free_order[i] : i;
+    p->head = 0; p->count = num_pages;
+    p->refcount = (int32_t*)calloc((size_t)num_pages, sizeof(int32_t));
+    p->table = (int32_t*)malloc(sizeof(int32_t) * (size_t)max_seqs * (size_t)max_pages);
+    for (int64_t i = 0; i < (int64_t)max_seqs * max_pages; ++i) p->table[i] = -1;
+    p->seq_len = (int32_t*)calloc((size_t)max_seqs, sizeof(int32_t));
+    p->seq_pages = (int32_t*)calloc((size_t)max_seqs, sizeof(int32_t));
+    p->seq_live = (int32_t*)calloc((size_t)max_seqs, sizeof(int32_t));
+    return p;
+}
+
+ORACLE_API void oracle_pool_destroy(oracle_pool* p) {
+    if (!p) return;
+    free(p->ring); free(p->refcount); free(p->table); free(p->seq_len); free(p->seq_pages); free(p->seq_live); free(p);
+}
+
+static int32_t pool_pop(oracle_pool* p) {
+    int32_t page = p->ring[p->head];
+    p->head = (p->head + 1) % p->num_pages; p->count--;
+    p->refcount[page] = 1;
+    return page;
+}
+
+static void pool_release(oracle_pool* p, int32_t page) {
+    if (--p->refcount[page] == 0) {
+        p->ring[(p->head + p->count) % p->num_pages] = page; p->count++;
+    }
+}
+
+/* Lowest free slot, or -1. */
+ORACLE_API int32_t oracle_pool_seq_create(oracle_pool* p) {
+    for (int32_t s = 0; s < p->max_seqs; ++s)
+        if (!p->seq_live[s]) { p->seq_live[s] = 1; p->seq_len[s] = 0; p->seq_pages[s] = 0; return s; }
+    return -1;
+}
+
+/* Reserve pages for n more tokens of `seq`; returns 0, or -1 when pages or table row run out. */
+ORACLE_API int32_t oracle_pool_append(oracle_pool* p, int32_t seq, int32_t n_tokens) {
+    int32_t new_len = p->seq_len[seq] + n_tokens;
+    int32_t need = (new_len + p->page_size - 1) / p->page_size;
+    if (need > p->max_pages || need - p->seq_pages[seq] > p->count) return -1;
+    while (p->seq_pages[seq] < need)
+        p->table[(int64_t)seq * p->max_pages + p->seq_pages[seq]++] = pool_pop(p);
+    p->seq_len[seq] = new_len;
+    return 0;
+}
+
+/* Shrink to new_len tokens, releasing pages from the back (paged_attention.cpp:397-418). */
+ORACLE_API void oracle_pool_truncate(oracle_pool* p, int32_t seq, int32_t new_len) {
+    if (new_len >= p->seq_len[seq]) return;
+    int32_t need = (new_len + p->page_size - 1) / p->page_size;
+    while (p->seq_pages[seq] > need) {
+        int64_t at = (int64_t)seq * p->max_pages + --p->seq_pages[seq];
+        pool_release(p, p->table[at]); p->table[at] = -1;
+    }
+    p->seq_len[seq] = new_len;
+}
+
+/* Release pages front to back (paged_attention.cpp:358-360) and free the slot. */
+ORACLE_API void oracle_pool_seq_destroy(oracle_pool* p, int32_t seq) {
+    for (int32_t i = 0; i < p->seq_pages[seq]; ++i) {
+        int64_t at = (int64_t)seq * p->max_pages + i;
+        pool_release(p, p->table[at]); p->table[at] = -1;
+    }
+    p->seq_pages[seq] = 0; p->seq_len[seq] = 0; p->seq_live[seq] = 0;
+}
+
+/*
+ * New sequence sharing the first floor(n_prefix / page_size) pages of `src`; the tokens of
+ * a partly filled last prefix page are copied into a fresh page owned by the new sequence.
+ * Returns the new slot (or -1); *copied_from / *copied_to name the pages of that copy
+ * (-1 when the prefix is page-aligned).
+ */
+ORACLE_API int32_t oracle_pool_fork(oracle_pool* p, int32_t src, int32_t n_prefix,
+                                    int32_t* copied_from, int32_t* copied_to) {
+    if (copied_from) *copied_from = -1;
+    if (copied_to) *copied_to = -1;
+    if (n_prefix > p->seq_len[src]) return -1;
+    int32_t full = n_prefix / p->page_size, rem = n_prefix % p->page_size;
+    if (rem && p->count < 1) return -1;
+    int32_t dst = oracle_pool_seq_create(p);
+    if (dst < 0) return -1;
+    for (int32_t i = 0; i < full; ++i) {
+        int32_t page = p->table[(int64_t)src * p->max_pages + i];
+        p->refcount[page]++;
+        p->table[(int64_t)dst * p->max_pages + i] = page;
+    }
+    p->seq_pages[dst] = full;
+    if (rem) {
+        int32_t page = pool_pop(p);
+        p->table[(int64_t)dst * p->max_pages + full] = page;
+        p->seq_pages[dst] = full + 1;
+        if (copied_from) *copied_from = p->table[(int64_t)src * p->max_pages + full];
+        if (copied_to) *copied_to = page;
+    }
+    p->seq_len[dst] = n_prefix;
+    return dst;
+}
+
+ORACLE_API int32_t oracle_pool_seq_len(const oracle_pool* p, int32_t seq) { return p->seq_len[seq]; }
+ORACLE_API int32_t oracle_pool_seq_pages(const oracle_pool* p, int32_t seq) { return p->seq_pages[seq]; }
+ORACLE_API int64_t oracle_pool_free_count(const oracle_pool* p) { return p->count; }
+ORACLE_API int32_t oracle_pool_refcount(const oracle_pool* p, int32_t page) { return p->refcount[page]; }
+ORACLE_API void oracle_pool_block_table(const oracle_pool* p, int32_t seq, int32_t* out, int32_t n) {
+    for (int32_t i = 0; i < n; ++i) out[i] = i < p->max_pages ? p->table[(int64_t)seq * p->max_pages + i] : -1;
+}

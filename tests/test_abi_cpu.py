@@ -1,0 +1,148 @@
+"""CPU tests of the boundary: the library loads, exports every symbol the header declares, and its
+host-side logic (argument validation, partition arithmetic) behaves; no compute without a GPU."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from attention_b200 import abi, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "ahpc.h")).read()
+    return sorted(set(re.findall(r"AHPC_API[^;(]*?\b(ahpc_\w+)\s*\(", text)))
+
+
+def test_header_and_binding_list_agree():
+    assert _header_symbols() == sorted(abi.EXPORTED_SYMBOLS)
+
+
+def test_library_exports_every_declared_symbol(native_lib):
+    for name in _header_symbols():
+        assert hasattr(native_lib, name), f"{name} is declared in include/ahpc.h but not exported"
+
+
+def test_version_and_error_string(native_lib):
+    assert re.fullmatch(r"\d+\.\d+\.\d+", native_lib.ahpc_version().decode())
+    a = abi.FaArgs()
+    assert native_lib.ahpc_fa_fwd(C.byref(a)) == 1                       # INVALID_INPUT: null tensors
+    assert b"NULL" in native_lib.ahpc_last_error_string()
+    assert native_lib.ahpc_fa_fwd(None) == 1
+
+
+def test_status_codes_match_attention_error_enum():
+    assert [abi.STATUS_NAMES[i] for i in range(8)] == [
+        "SUCCESS", "INVALID_INPUT", "INVALID_PARAMETERS", "MEMORY_ALLOCATION_FAILED", "COMPUTATION_FAILED",
+        "BACKEND_NOT_AVAILABLE", "UNSUPPORTED_OPERATION", "INTERNAL_ERROR"]
+
+
+def test_fa_argument_validation(native_lib):
+    buf = (C.c_float * 16)()
+    a = abi.FaArgs()
+    a.q = a.k = a.v = a.out = C.addressof(buf)
+    a.dtype = 0
+    a.batch, a.heads, a.seq_q, a.seq_kv, a.head_dim = 1, 1, 0, 1, 4      # zero dimension
+    assert native_lib.ahpc_fa_fwd(C.byref(a)) == 2
+    a.seq_q = 1
+    a.dtype = 9
+    assert native_lib.ahpc_fa_fwd(C.byref(a)) == 2
+    a.dtype = 0
+    a.kernel = 5
+    assert native_lib.ahpc_fa_fwd(C.byref(a)) == 2
+    a.kernel = 0
+    a.q_strides = (C.c_int64 * 4)(-1, 0, 0, 0)
+    assert native_lib.ahpc_fa_fwd(C.byref(a)) == 2
+
+
+def test_no_cpu_fallback(native_lib):
+    """With no device, a well-formed call must fail with BACKEND_NOT_AVAILABLE, never compute."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    assert native_lib.ahpc_device_count() == 0
+    buf = (C.c_float * 16)()
+    out = (C.c_float * 16)(*([7.0] * 16))
+    a = abi.FaArgs()
+    a.q = a.k = a.v = C.addressof(buf)
+    a.out = C.addressof(out)
+    a.batch, a.heads, a.seq_q, a.seq_kv, a.head_dim = 1, 1, 2, 2, 4
+    a.q_strides = a.k_strides = a.v_strides = a.o_strides = (C.c_int64 * 4)(8, 8, 4, 1)
+    assert native_lib.ahpc_fa_fwd(C.byref(a)) == 5
+    assert list(out) == [7.0] * 16
+    cfg = abi.PoolConfig(0, 1, 4, 16, 2, 64, 2, 4, None)
+    p = C.c_void_p()
+    assert native_lib.ahpc_pool_create(C.byref(p), C.byref(cfg)) == 5 and not p.value
+
+
+def test_pool_config_validation(native_lib):
+    p = C.c_void_p()
+    bad = abi.PoolConfig(0, 1, 4, 16, 2, 60, 2, 4, None)                # head_dim not a multiple of 8
+    assert native_lib.ahpc_pool_create(C.byref(p), C.byref(bad)) == 2
+    order = (C.c_int32 * 4)(0, 1, 1, 3)                                  # not a permutation
+    bad = abi.PoolConfig(0, 1, 4, 16, 2, 64, 2, 4, order)
+    assert native_lib.ahpc_pool_create(C.byref(p), C.byref(bad)) == 2
+    assert native_lib.ahpc_pool_create(None, None) == 1
+
+
+def test_strides(native_lib):
+    assert abi.fa_strides(abi.LAYOUT_BHSD, 2, 8, 512, 64) == (8 * 512 * 64, 512 * 64, 64, 1)
+    assert abi.fa_strides(abi.LAYOUT_BSHD, 2, 8, 512, 64) == (512 * 8 * 64, 64, 8 * 64, 1)
+    with pytest.raises(abi.AhpcError):
+        abi.fa_strides(7, 1, 1, 1, 1)
+
+
+@pytest.mark.parametrize("units,world", [(16, 1), (16, 8), (128, 8), (10, 4), (3, 8), (0, 2)])
+def test_shard_range_partitions_exactly(native_lib, units, world):
+    ranges = [abi.shard_range(units, world, r) for r in range(world)]
+    assert ranges[0][0] == 0 and ranges[-1][1] == units
+    sizes = [e - b for b, e in ranges]
+    assert all(ranges[i][1] == ranges[i + 1][0] for i in range(world - 1))
+    assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+    with pytest.raises(abi.AhpcError):
+        abi.shard_range(units, world, world)
+
+
+def test_workspace_bytes(native_lib):
+    assert native_lib.ahpc_fa_workspace_bytes(0, 2, 8, 512, 512, 64, 0) == 4 * 2 * 8 * 512 * 64 * 4
+    assert native_lib.ahpc_fa_workspace_bytes(2, 1, 1, 8, 16, 64, 1) == 2 * 8 * 64 * 2 + 2 * 16 * 64 * 2 + 8 * 16 * 4
+    assert native_lib.ahpc_fa_workspace_bytes(5, 1, 1, 1, 1, 1, 0) == 0
+
+
+# ---- synthetic workloads (host logic of the benchmark) ----------------------------------------
+
+def test_context_lengths_are_seeded_and_in_range():
+    for cfg in (synth.C3, synth.C5):
+        a, b = synth.context_lengths(cfg), synth.context_lengths(cfg)
+        assert np.array_equal(a, b) and len(a) == cfg.batch
+        assert a.min() >= cfg.ctx_lo and a.max() <= cfg.ctx_hi
+    assert abs(synth.context_lengths(synth.C3).mean() - 4352) < 900
+
+
+def test_page_permutation():
+    p = synth.page_permutation(1000, 5)
+    assert sorted(p) == list(range(1000)) and not np.array_equal(p, np.arange(1000))
+    assert np.array_equal(p, synth.page_permutation(1000, 5))
+
+
+def test_sharing_plan_hits_the_target_fraction():
+    plan = synth.sharing_plan(synth.C5)
+    assert 0.08 <= plan.shared_fraction <= 0.12
+    assert np.all(plan.prefix_tokens % synth.C5.page_size == 0)
+    assert np.all(plan.prefix_tokens <= plan.ctx)
+    leaders = plan.group_leader == np.arange(len(plan.ctx))
+    assert np.all(plan.prefix_tokens[leaders] == 0)
+    by = synth.decode_algorithmic_bytes(synth.C5, plan)
+    assert by["kv_unique"] < by["kv_logical"]
+    assert by["kv_logical"] == int(plan.ctx.astype(np.int64).sum()) * 16384
+    none = synth.sharing_plan(synth.C3)
+    assert none.shared_refs == 0
+
+
+def test_flop_counts():
+    assert synth.C1.flops == 4 * 2 * 8 * 512 * 512 * 64
+    assert synth.C2.flops == 4 * 4 * 32 * 4096 * 4096 * 128 / 2
+    assert synth.C4.flops == 4 * 1 * 16 * 32768 * 32768 * 128 / 2

@@ -1,0 +1,236 @@
+"""CPU tests of the oracle itself: against the reference project's own checker (oracle/_ref),
+against the committed golden fixtures made with it, and through properties."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import cpu_oracle as o
+from tests.golden import make_golden as g
+
+REF = pytest.mark.skipif(not o.ref_available(), reason="oracle/_ref not built and reference tree absent")
+
+
+def _rand(shape, seed, lo=-1.0, hi=1.0):
+    return np.random.default_rng(seed).uniform(lo, hi, shape).astype(np.float32)
+
+
+# ---- pinned against the reference's own checker -------------------------------------------------
+
+@REF
+@pytest.mark.parametrize("S", [1, 4, 16, 32, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_oracle_matches_reference_checker_seq(S, causal):
+    B, H, D = 2, 4, 64                                   # tests/test_flash_attention.cpp:103-106, 219
+    q, k, v = (_rand((B, H, S, D), 10 * S + i) for i in range(3))
+    scale = 1.0 / np.sqrt(D)
+    got = o.attention_fwd(q, k, v, scale, causal)
+    ref = o.ref_attention(q, k, v, scale, causal)
+    assert np.abs(got - ref).max() <= 2e-6              # the checker accumulates in float
+
+
+@REF
+@pytest.mark.parametrize("D", [16, 32, 64, 128])
+def test_oracle_matches_reference_checker_dim(D):
+    B, H, S = 2, 4, 16                                   # tests/test_flash_attention.cpp:264
+    q, k, v = (_rand((B, H, S, D), 7 * D + i) for i in range(3))
+    scale = 1.0 / np.sqrt(D)
+    assert np.abs(o.attention_fwd(q, k, v, scale) - o.ref_attention(q, k, v, scale, False)).max() <= 2e-6
+
+
+@REF
+def test_oracle_matches_reference_checker_mask():
+    B, H, S, D = 2, 4, 16, 64                            # tests/test_flash_attention.cpp:483-582
+    q, k, v = (_rand((B, H, S, D), 50 + i) for i in range(3))
+    mask = np.zeros((B, S, S), np.float32)
+    mask[:, :, : S // 2] = 1.0
+    got = o.attention_fwd(q, k, v, 0.125, False, mask)
+    assert np.abs(got - o.ref_masked_attention(q, k, v, mask, 0.125)).max() <= 2e-6
+
+
+@REF
+def test_oracle_matches_reference_checker_c1_shape():
+    """BASELINE configuration 1 (FP32, B2 S512 H8 D64, N(0,1)) on a head subset."""
+    rng = np.random.default_rng(1000)
+    q, k, v = (rng.standard_normal((1, 2, 512, 64)).astype(np.float32) for _ in range(3))
+    got = o.attention_fwd(q, k, v, 0.125)
+    assert np.abs(got - o.ref_attention(q, k, v, 0.125, False)).max() <= 1e-5
+
+
+# ---- pinned against the committed fixtures ------------------------------------------------------
+
+@pytest.mark.parametrize("name", sorted(g.CASES))
+def test_oracle_matches_golden(name):
+    fx = np.load(g.FIXTURE)
+    q, k, v, mask, scale, causal = g.case_inputs(name)
+    assert bytes(fx[name + "__sha"]).decode() == g.inputs_digest(q, k, v, mask), "input generator drifted"
+    got = o.attention_fwd(q, k, v, scale, causal, mask)
+    B, H, S, D = q.shape
+    tol = max(1e-4, 1e-5 * np.sqrt(D))                   # tests/test_flash_attention.cpp:303
+    assert np.abs(got - fx[name]).max() <= tol
+    assert np.abs(got - fx[name]).max() <= 2e-6
+
+
+def test_f32acc_port_matches_oracle():
+    q, k, v = (_rand((2, 3, 70, 32), 90 + i) for i in range(3))
+    for causal in (False, True):
+        a = o.attention_fwd(q, k, v, 0.2, causal)
+        b = o.attention_fwd_f32acc(q, k, v, 0.2, causal, threads=2)
+        assert np.abs(a - b).max() <= 1e-5
+
+
+# ---- properties ------------------------------------------------------------------------------
+
+def test_softmax_properties():
+    B, H, S, D = 1, 2, 33, 16
+    q, k, v = (_rand((B, H, S, D), 5 + i) for i in range(3))
+    # S = 1  =>  O = V
+    assert np.allclose(o.attention_fwd(q[:, :, :1], k[:, :, :1], v[:, :, :1], 0.25), v[:, :, :1], atol=1e-7)
+    # causal: row 0 sees only key 0
+    out = o.attention_fwd(q, k, v, 0.25, True)
+    assert np.allclose(out[:, :, 0], v[:, :, 0], atol=1e-7)
+    # constant V  =>  O = that constant (weights sum to 1)
+    vc = np.full_like(v, 0.75)
+    assert np.allclose(o.attention_fwd(q, k, vc, 0.25), 0.75, atol=1e-6)
+    # lse is log(sum(exp(score)))
+    out, lse = o.attention_fwd(q, k, v, 0.25, return_lse=True)
+    s = np.einsum("bhid,bhjd->bhij", q.astype(np.float64), k.astype(np.float64)) * 0.25
+    assert np.allclose(lse, np.log(np.exp(s).sum(-1)), atol=1e-5)
+
+
+def test_fully_masked_row_is_zero():
+    q, k, v = (_rand((1, 1, 4, 8), 20 + i) for i in range(3))
+    mask = np.ones((1, 4, 4), np.float32)
+    mask[0, 2, :] = 0.0
+    out = o.attention_fwd(q, k, v, 1.0, False, mask)
+    assert np.all(out[0, 0, 2] == 0.0) and np.all(np.isfinite(out))
+
+
+def test_strided_views_equal_contiguous():
+    B, H, S, D = 2, 3, 9, 16
+    bshd = [_rand((B, S, H, D), 30 + i) for i in range(3)]
+    views = [x.transpose(0, 2, 1, 3) for x in bshd]                       # [B,H,S,D] views of [B,S,H,D] memory
+    dense = [np.ascontiguousarray(x) for x in views]
+    assert np.array_equal(o.attention_fwd(*views, 0.3, True), o.attention_fwd(*dense, 0.3, True))
+
+
+def test_rectangular_attention():
+    q = _rand((1, 2, 5, 8), 40)
+    k, v = _rand((1, 2, 11, 8), 41), _rand((1, 2, 11, 8), 42)
+    out = o.attention_fwd(q, k, v, 0.5)
+    s = np.einsum("bhid,bhjd->bhij", q, k).astype(np.float64) * 0.5
+    w = np.exp(s - s.max(-1, keepdims=True))
+    w /= w.sum(-1, keepdims=True)
+    assert np.allclose(out, np.einsum("bhij,bhjd->bhid", w, v), atol=1e-6)
+
+
+# ---- 16-bit payloads ---------------------------------------------------------------------------
+
+def test_converters_match_numpy_and_roundtrip():
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal(200000) * np.exp(rng.uniform(-24, 13, 200000))).astype(np.float32)
+    x[:6] = [0.0, -0.0, np.inf, -np.inf, 65504.0, 65520.0]
+    h = o.round_to(x, "f16")
+    assert np.array_equal(h, x.astype(np.float16).view(np.uint16))       # numpy rounds to nearest even
+    assert np.array_equal(o.widen(h, "f16"), x.astype(np.float16).astype(np.float32))
+    b = o.round_to(x, "bf16")
+    back = o.widen(b, "bf16")
+    assert np.array_equal(o.round_to(back, "bf16"), b)                   # idempotent
+    fin = np.isfinite(x) & np.isfinite(back)
+    assert np.all(np.abs(back[fin] - x[fin]) <= np.abs(x[fin]) * 2.0 ** -8)
+    # ties to even: 1 + 2^-8 is halfway between bf16(1) and the next value
+    assert o.round_to(np.array([1.0 + 2.0 ** -8], np.float32), "bf16")[0] == 0x3F80
+    assert o.round_to(np.array([1.0 + 3 * 2.0 ** -8], np.float32), "bf16")[0] == 0x3F82
+
+
+# ---- paged decode ------------------------------------------------------------------------------
+
+def _paged_case(seed, n_seqs, H, D, ps, lens, num_pages):
+    rng = np.random.default_rng(seed)
+    order = rng.permutation(num_pages).astype(np.int32)
+    pool = o.PoolModel(num_pages, ps, n_seqs, max(1, (max(lens) + ps - 1) // ps), free_order=order)
+    kc = np.zeros((num_pages, ps, H, D), np.float32)
+    vc = np.zeros_like(kc)
+    ks, vs = [], []
+    for L in lens:
+        s = pool.seq_create()
+        assert pool.append(s, int(L)) == 0
+        k = rng.standard_normal((L, H, D)).astype(np.float32)
+        v = rng.standard_normal((L, H, D)).astype(np.float32)
+        bt = pool.block_table(s)
+        for t in range(L):
+            kc[bt[t // ps], t % ps] = k[t]
+            vc[bt[t // ps], t % ps] = v[t]
+        ks.append(k)
+        vs.append(v)
+    q = rng.standard_normal((n_seqs, H, D)).astype(np.float32)
+    table = np.stack([pool.block_table(s) for s in range(n_seqs)])
+    return q, kc, vc, table, np.asarray(lens, np.int32), ks, vs
+
+
+def test_paged_decode_equals_dense_on_gathered_kv():
+    lens = [1, 15, 16, 17, 100, 0]
+    q, kc, vc, table, sl, ks, vs = _paged_case(11, len(lens), 3, 32, 16, lens, 64)
+    scale = 1.0 / np.sqrt(32)
+    got = o.paged_decode(q, kc, vc, table, sl, scale)
+    for i, L in enumerate(lens):
+        if L == 0:
+            assert np.all(got[i] == 0)
+            continue
+        dense = o.attention_fwd(q[i][None, :, None, :], ks[i].transpose(1, 0, 2)[None], vs[i].transpose(1, 0, 2)[None], scale)
+        assert np.abs(got[i] - dense[0, :, 0]).max() <= 1e-6
+    port = o.paged_decode_f32acc(q, kc, vc, "f32", table, sl, scale, threads=2)
+    assert np.abs(port - got).max() <= 1e-5
+
+
+def test_paged_decode_stops_at_negative_table_entry():
+    q, kc, vc, table, sl, ks, vs = _paged_case(12, 1, 2, 16, 4, [10], 8)
+    cut = table.copy()
+    cut[0, 1] = -1                                              # walk ends after the first page (4 tokens)
+    got = o.paged_decode(q, kc, vc, cut, sl, 0.25)
+    dense = o.attention_fwd(q[0][None, :, None, :], ks[0][:4].transpose(1, 0, 2)[None], vs[0][:4].transpose(1, 0, 2)[None], 0.25)
+    assert np.abs(got[0] - dense[0, :, 0]).max() <= 1e-6
+
+
+# ---- allocator model ---------------------------------------------------------------------------
+
+def test_pool_model_fifo_order_and_reuse():
+    p = o.PoolModel(8, 4, 4, 4)
+    a, b = p.seq_create(), p.seq_create()
+    assert (a, b) == (0, 1)
+    assert p.append(a, 5) == 0 and list(p.block_table(a)) == [0, 1, -1, -1]
+    assert p.append(b, 4) == 0 and list(p.block_table(b)) == [2, -1, -1, -1]
+    assert p.append(a, 3) == 0 and list(p.block_table(a)) == [0, 1, -1, -1]      # 8 tokens fit 2 pages
+    assert p.append(a, 1) == 0 and list(p.block_table(a)) == [0, 1, 3, -1]
+    assert p.free_count() == 4
+    p.truncate(a, 4)                                                           # releases 3 then 1 (from the back)
+    assert list(p.block_table(a)) == [0, -1, -1, -1] and p.free_count() == 6
+    c = p.seq_create()
+    assert p.append(c, 16) == 0 and list(p.block_table(c)) == [4, 5, 6, 7]     # FIFO: old free pages first
+    assert p.append(b, 5) == 0 and list(p.block_table(b)) == [2, 3, 1, -1]     # then the returned ones, in push order
+    assert p.append(a, 1) == -1                                                 # pool exhausted, nothing changes
+    assert p.seq_len(a) == 4
+    p.seq_destroy(c)
+    assert p.free_count() == 4 and p.seq_create() == c
+
+
+def test_pool_model_table_row_limit():
+    p = o.PoolModel(16, 4, 1, 2)
+    s = p.seq_create()
+    assert p.append(s, 8) == 0
+    assert p.append(s, 1) == -1
+
+
+def test_pool_model_fork_shares_whole_pages():
+    p = o.PoolModel(8, 4, 4, 4, free_order=[5, 3, 7, 1, 0, 2, 4, 6])
+    a = p.seq_create()
+    assert p.append(a, 10) == 0 and list(p.block_table(a)) == [5, 3, 7, -1]
+    b, frm, to = p.fork(a, 9)                                 # two whole pages shared, one token copied
+    assert list(p.block_table(b)) == [5, 3, 1, -1] and (frm, to) == (7, 1)
+    assert [p.refcount(x) for x in (5, 3, 7, 1)] == [2, 2, 1, 1]
+    p.seq_destroy(a)                                          # shared pages stay; only page 7 returns
+    assert p.free_count() == 5 and p.refcount(5) == 1
+    p.seq_destroy(b)
+    assert p.free_count() == 8
+    c, frm, to = p.fork(p.seq_create(), 0)
+    assert (frm, to) == (-1, -1)
