@@ -1,0 +1,117 @@
+"""GPU parity of the FlashAttention forward against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from attention_b200 import abi, ops, synth
+from oracle import cpu_oracle as o
+from tests import gpu_util as u
+from tests.golden import make_golden as g
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_case(B, H, Sq, Skv, D, dtype, causal, seed, *, kernel=abi.KERNEL_AUTO, mask=None, layout="BHSD",
+             host=False, in_scale=1.0, scale=None):
+    scale = (1.0 / np.sqrt(D)) if scale is None else scale
+    (q,), (tq,) = u.rounded_inputs((B, H, Sq, D), dtype, seed, in_scale, 1)
+    (k, v), (tk, tv) = u.rounded_inputs((B, H, Skv, D), dtype, seed + 1, in_scale, 2)
+    want = o.attention_fwd(q, k, v, scale, causal, mask)
+    if dtype != "f32":
+        pass  # the oracle consumed the rounded inputs; the output is compared before rounding
+    if layout == "BSHD":   # same logical values, memory stored [B,S,H,D]
+        tq, tk, tv = (t.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3) for t in (tq, tk, tv))
+    tm = torch.from_numpy(mask) if mask is not None else None
+    if not host:
+        tq, tk, tv = tq.to(DEV), tk.to(DEV), tv.to(DEV)
+        tm = tm.to(DEV) if tm is not None else None
+    out = ops.flash_attention_forward(tq, tk, tv, causal=causal, scale=scale, mask=tm, kernel=kernel)
+    assert out.stride() == tq.stride()
+    u.assert_close(u.torch_to_f32(out), want, dtype, f"B{B} H{H} Sq{Sq} Skv{Skv} D{D} {dtype} causal={causal}")
+    return out
+
+
+# ---- the reference's own test cases (tests/test_flash_attention.cpp) ----------------------------
+
+@pytest.mark.parametrize("name", sorted(g.CASES))
+def test_golden_cases_fp32(name):
+    """Against outputs of the reference's checker stored in tests/golden (tolerance of the reference's
+    tests: max(1e-4, 1e-5*sqrt(D)), tests/test_flash_attention.cpp:174,303)."""
+    fx = np.load(g.FIXTURE)
+    q, k, v, mask, scale, causal = g.case_inputs(name)
+    tq, tk, tv = (torch.from_numpy(x).to(DEV) for x in (q, k, v))
+    tm = torch.from_numpy(mask).to(DEV) if mask is not None else None
+    out = ops.flash_attention_forward(tq, tk, tv, causal=causal, scale=scale, mask=tm)
+    tol = max(1e-4, 1e-5 * np.sqrt(q.shape[-1]))
+    assert np.abs(u.torch_to_f32(out) - fx[name]).max() <= tol
+
+
+def test_host_pointers_like_the_reference_tests():
+    """The reference's tests pass host vectors (ForwardPassSmallInput, :141-175)."""
+    run_case(2, 4, 16, 16, 64, "f32", False, 1, host=True)
+    run_case(2, 4, 16, 16, 64, "f32", True, 2, host=True)
+
+
+@pytest.mark.parametrize("S", [1, 4, 16, 17, 63, 64, 65, 127, 128, 129, 512])
+@pytest.mark.parametrize("causal", [False, True])
+def test_simt_fp32_sequence_lengths(S, causal):
+    run_case(2, 4, S, S, 64, "f32", causal, 10 + S, kernel=abi.KERNEL_SIMT)
+
+
+@pytest.mark.parametrize("D", [16, 32, 64, 128, 8, 20, 72, 256])
+def test_simt_fp32_head_dims(D):
+    run_case(2, 3, 33, 33, D, "f32", False, 100 + D, kernel=abi.KERNEL_SIMT)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_simt_16bit(dtype, causal):
+    run_case(2, 3, 130, 130, 64, dtype, causal, 7, kernel=abi.KERNEL_SIMT)
+
+
+def test_simt_rectangular_and_scale():
+    run_case(1, 2, 50, 200, 32, "f32", False, 5, kernel=abi.KERNEL_SIMT, scale=0.3)
+    run_case(1, 2, 200, 50, 32, "f32", True, 6, kernel=abi.KERNEL_SIMT)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_mask_half_and_fully_masked_rows(dtype):
+    B, S = 2, 70
+    rng = np.random.default_rng(3)
+    mask = (rng.random((B, S, S)) < 0.5).astype(np.float32)
+    mask[0, 5, :] = 0.0                                   # a row with no visible key -> zeros
+    out = run_case(B, 3, S, S, 64, dtype, False, 9, mask=mask)
+    assert torch.all(out[0, :, 5, :] == 0)
+    run_case(B, 3, S, S, 64, dtype, True, 9, mask=mask)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_bshd_memory_order(dtype):
+    run_case(2, 4, 100, 100, 64, dtype, True, 21, layout="BSHD")
+
+
+def test_c1_full_fp32():
+    """BASELINE configuration 1 in full: FP32 non-causal B2 S512 H8 D64, N(0,1), scale 1/8."""
+    c = synth.C1
+    run_case(c.batch, c.heads, c.seq, c.seq, c.head_dim, "f32", c.causal, c.seed)
+
+
+def test_lse_output():
+    B, H, S, D = 1, 2, 40, 32
+    (q, k, v), (tq, tk, tv) = u.rounded_inputs((B, H, S, D), "f32", 4)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=DEV)
+    ops.flash_attention_forward(tq.to(DEV), tk.to(DEV), tv.to(DEV), causal=True, scale=0.2, lse=lse, kernel=abi.KERNEL_SIMT)
+    _, want = o.attention_fwd(q, k, v, 0.2, True, return_lse=True)
+    assert np.abs(lse.cpu().numpy() - want).max() <= 1e-4
+
+
+def test_error_statuses_on_gpu():
+    t = torch.zeros((1, 1, 4, 24), device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(abi.AhpcError) as e:                # D=24 is not a tensor-core shape
+        ops.flash_attention_forward(t, t, t, kernel=abi.KERNEL_TC)
+    assert e.value.status == 6
+    big = torch.zeros((1, 1, 4, 512), device=DEV)
+    with pytest.raises(abi.AhpcError) as e:
+        ops.flash_attention_forward(big, big, big)
+    assert e.value.status == 6

@@ -1,0 +1,225 @@
+"""GPU parity of the paged KV pool (bit-exact block tables against the CPU allocator model) and of
+the PagedAttention decode against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from attention_b200 import abi, ops, synth
+from oracle import cpu_oracle as o
+from tests import gpu_util as u
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+class Mirror:
+    """Drives the device pool and the CPU model with the same calls and keeps the canonical
+    [num_pages, page_size, H, D] caches the oracle's decode reads."""
+
+    def __init__(self, *, num_pages, heads, head_dim, dtype="f16", page_size=16, max_seqs=8, max_pages=64, seed=0, permute=True):
+        order = synth.page_permutation(num_pages, seed) if permute else None
+        self.dtype = dtype
+        self.pool = ops.KVPool(num_pages=num_pages, heads=heads, head_dim=head_dim, dtype=u.TORCH_DTYPE[dtype], page_size=page_size,
+                               max_seqs=max_seqs, max_pages_per_seq=max_pages, free_order=order)
+        self.model = o.PoolModel(num_pages, page_size, max_seqs, max_pages, free_order=order)
+        self.kc = np.zeros((num_pages, page_size, heads, head_dim), np.float32)
+        self.vc = np.zeros_like(self.kc)
+        self.rng = np.random.default_rng(seed)
+        self.H, self.D, self.ps = heads, head_dim, page_size
+
+    def create(self):
+        a, b = self.pool.seq_create(), self.model.seq_create()
+        assert a == b
+        return a
+
+    def append(self, seqs, counts, host=False):
+        ks, vs = [], []
+        for s, n in zip(seqs, counts):
+            start = self.model.seq_len(s)
+            assert self.model.append(s, n) == 0
+            k = o.round_to(self.rng.standard_normal((n, self.H, self.D)).astype(np.float32), self.dtype)
+            v = o.round_to(self.rng.standard_normal((n, self.H, self.D)).astype(np.float32), self.dtype)
+            bt = self.model.block_table(s)
+            kf, vf = o.widen(k, self.dtype), o.widen(v, self.dtype)
+            for t in range(n):
+                self.kc[bt[(start + t) // self.ps], (start + t) % self.ps] = kf[t]
+                self.vc[bt[(start + t) // self.ps], (start + t) % self.ps] = vf[t]
+            ks.append(k)
+            vs.append(v)
+        tk = u.payload_to_torch(np.concatenate(ks), self.dtype)
+        tv = u.payload_to_torch(np.concatenate(vs), self.dtype)
+        if not host:
+            tk, tv = tk.to(DEV), tv.to(DEV)
+        self.pool.append(seqs, counts, tk, tv)
+
+    def check_tables(self):
+        for s in range(self.model.max_seqs):
+            assert np.array_equal(self.pool.block_table(s), self.model.block_table(s)), f"block table of sequence {s}"
+        lens = self.pool.seq_lens()
+        for s in range(self.model.max_seqs):
+            assert lens[s] == self.model.seq_len(s)
+        ref = np.array([self.model.refcount(p) for p in range(self.model.num_pages)], np.int32)
+        assert np.array_equal(self.pool.refcounts(), ref)
+        assert len(self.pool.free_ring()) == self.model.free_count()
+        assert self.pool.error_flag() == 0
+
+    def decode_check(self, seqs, qo_dtype=None, split=0, host=False, scale=0.0):
+        qo_dtype = qo_dtype or self.dtype
+        n = len(seqs)
+        q = o.round_to(self.rng.standard_normal((n, self.H, self.D)).astype(np.float32), qo_dtype)
+        tq = u.payload_to_torch(q, qo_dtype)
+        if not host:
+            tq = tq.to(DEV)
+        out = self.pool.decode(seqs, tq, split_tokens=split, scale=scale)
+        table = np.stack([self.model.block_table(s) for s in seqs])
+        lens = np.array([self.model.seq_len(s) for s in seqs], np.int32)
+        sc = scale if scale else 1.0 / np.sqrt(self.D)
+        want = o.paged_decode(o.widen(q, qo_dtype), self.kc, self.vc, table, lens, sc)
+        u.assert_close(u.torch_to_f32(out), want, qo_dtype, f"decode lens={list(lens)} split={split}")
+        return out
+
+
+def test_block_tables_bit_exact_through_a_call_history():
+    m = Mirror(num_pages=40, heads=2, head_dim=64, max_seqs=6, max_pages=12, seed=1)
+    a, b, c = m.create(), m.create(), m.create()
+    m.append([a, b, c], [5, 16, 33])
+    m.check_tables()
+    m.append([c, a], [1, 30])                      # call order decides who gets which pages
+    m.check_tables()
+    m.pool.seq_truncate(c, 17)
+    m.model.truncate(c, 17)
+    m.check_tables()
+    m.pool.seq_destroy(b)
+    m.model.seq_destroy(b)
+    m.check_tables()
+    d = m.create()
+    assert d == b
+    m.append([d], [100])
+    m.check_tables()
+    # refused calls change nothing: a row that would overflow the table, then a drained pool
+    z = torch.zeros((16 * 13, 2, 64), dtype=torch.float16, device=DEV)
+    with pytest.raises(abi.AhpcError) as e:
+        m.pool.append([c], [16 * 13], z, z)
+    assert e.value.status == 3
+    free = m.model.free_count()
+    e1, e2, e3 = m.create(), m.create(), m.create()
+    z = torch.zeros((3 * 16 * 12, 2, 64), dtype=torch.float16, device=DEV)
+    assert 3 * 12 > free
+    with pytest.raises(abi.AhpcError) as e:
+        m.pool.append([e1, e2, e3], [16 * 12] * 3, z, z)
+    assert e.value.status == 3
+    m.check_tables()
+
+
+def test_free_ring_order_matches_model_after_releases():
+    m = Mirror(num_pages=16, heads=1, head_dim=64, max_seqs=4, max_pages=8, seed=2, permute=False)
+    a, b = m.create(), m.create()
+    m.append([a, b], [40, 50])
+    m.pool.seq_truncate(a, 10)
+    m.model.truncate(a, 10)
+    m.pool.seq_destroy(b)
+    m.model.seq_destroy(b)
+    c = m.create()
+    m.append([c], [16 * 8])                        # takes pages from the ring in its new order
+    m.check_tables()
+
+
+def test_fork_shares_pages_and_copies_the_partial_page():
+    m = Mirror(num_pages=32, heads=2, head_dim=64, max_seqs=4, max_pages=8, seed=3)
+    a = m.create()
+    m.append([a], [45])
+    b = m.pool.seq_fork(a, 37)
+    bm, frm, to = m.model.fork(a, 37)
+    assert b == bm
+    m.kc[to, : 37 % 16] = m.kc[frm, : 37 % 16]
+    m.vc[to, : 37 % 16] = m.vc[frm, : 37 % 16]
+    m.check_tables()
+    m.append([b], [20])
+    m.check_tables()
+    m.decode_check([a, b])
+    m.pool.seq_destroy(a)
+    m.model.seq_destroy(a)
+    m.check_tables()
+    m.decode_check([b])
+
+
+def test_append_gather_round_trip_and_host_tensors():
+    m = Mirror(num_pages=16, heads=3, head_dim=64, dtype="bf16", max_seqs=2, max_pages=8, seed=4)
+    a = m.create()
+    m.append([a], [21], host=True)
+    m.append([a], [30])
+    k, v = m.pool.gather(a, 3, 40)
+    bt = m.model.block_table(a)
+    want_k = np.stack([m.kc[bt[t // 16], t % 16] for t in range(3, 43)])
+    want_v = np.stack([m.vc[bt[t // 16], t % 16] for t in range(3, 43)])
+    assert np.array_equal(u.torch_to_f32(k), want_k) and np.array_equal(u.torch_to_f32(v), want_v)
+    kh, vh = m.pool.gather(a, 0, 51, dtype=torch.float32, device="cpu")
+    assert np.array_equal(kh.numpy()[3:43], want_k)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("D", [64, 128])
+def test_decode_edge_context_lengths(dtype, D):
+    lens = [1, 15, 16, 17, 511, 512, 513, 1000]
+    m = Mirror(num_pages=200, heads=4, head_dim=D, dtype=dtype, max_seqs=8, max_pages=64, seed=5)
+    seqs = [m.create() for _ in lens]
+    m.append(seqs, lens)
+    m.check_tables()
+    m.decode_check(seqs)
+    m.decode_check(seqs, split=64)
+    m.decode_check(seqs, split=1024)
+    m.decode_check(seqs[::-1] + seqs[:2], host=True)      # any order, duplicates allowed
+
+
+def test_decode_empty_sequence_gives_zeros():
+    m = Mirror(num_pages=8, heads=2, head_dim=64, max_seqs=2, max_pages=4, seed=6)
+    a, b = m.create(), m.create()
+    m.append([a], [9])
+    out = m.decode_check([a, b])
+    assert torch.all(out[1] == 0)
+
+
+def test_decode_mixed_query_dtype_and_scale():
+    m = Mirror(num_pages=32, heads=2, head_dim=128, dtype="f16", max_seqs=2, max_pages=16, seed=7)
+    a = m.create()
+    m.append([a], [200])
+    m.decode_check([a], qo_dtype="f32", scale=0.05)
+    m.decode_check([a], qo_dtype="bf16")
+
+
+@pytest.mark.parametrize("cfg", [dict(dtype="f32", D=64, ps=16), dict(dtype="f16", D=32, ps=16), dict(dtype="f16", D=128, ps=8),
+                                 dict(dtype="bf16", D=256, ps=32)])
+def test_decode_general_path(cfg):
+    m = Mirror(num_pages=64, heads=2, head_dim=cfg["D"], dtype=cfg["dtype"], page_size=cfg["ps"], max_seqs=4, max_pages=64, seed=8)
+    lens = [1, cfg["ps"] + 1, 300]
+    seqs = [m.create() for _ in lens]
+    m.append(seqs, lens)
+    m.check_tables()
+    m.decode_check(seqs, qo_dtype="f32" if cfg["dtype"] == "f32" else None)
+    m.decode_check(seqs, split=cfg["ps"] * 4, qo_dtype="f32" if cfg["dtype"] == "f32" else None)
+
+
+def test_c3_shaped_decode_sample():
+    """Configuration 3's shape on a sample of its sequences: FP16, H32 D128 page 16, contexts drawn
+    like the benchmark's, pages dealt from the seeded permutation."""
+    c = synth.C3
+    lens = [int(x) for x in synth.context_lengths(c)[:6]]
+    pages = sum((L + 15) // 16 for L in lens) + 8
+    m = Mirror(num_pages=pages, heads=c.heads, head_dim=c.head_dim, dtype="f16", max_seqs=8, max_pages=512, seed=c.seed)
+    seqs = [m.create() for _ in lens]
+    for s, L in zip(seqs, lens):
+        m.append([s], [L])
+    m.check_tables()
+    bt = m.pool.block_table(seqs[0], 8)
+    assert not np.array_equal(np.diff(bt), np.ones(7, np.int32))     # non-contiguous by construction
+    m.decode_check(seqs)
+
+
+def test_unknown_sequence_is_rejected():
+    pool = ops.KVPool(num_pages=4, heads=1, head_dim=64, max_seqs=2, max_pages_per_seq=4)
+    q = torch.zeros((1, 1, 64), dtype=torch.float16, device=DEV)
+    with pytest.raises(abi.AhpcError) as e:                    # "Sequence not found" (paged_attention.cpp:439-441)
+        pool.decode([1], q)
+    assert e.value.status == 1
+    with pytest.raises(abi.AhpcError):
+        pool.append([0], [1], q, q)
