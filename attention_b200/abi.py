@@ -24,6 +24,7 @@ STATUS_NAMES = {
 EXPORTED_SYMBOLS = [
     "ahpc_version", "ahpc_last_error_string", "ahpc_device_count", "ahpc_get_device_info",
     "ahpc_fa_strides", "ahpc_fa_fwd", "ahpc_fa_workspace_bytes", "ahpc_fa_select_kernel",
+    "ahpc_fa_read_error_word",
     "ahpc_pool_create", "ahpc_pool_destroy", "ahpc_pool_seq_create", "ahpc_pool_seq_destroy",
     "ahpc_pool_seq_truncate", "ahpc_pool_seq_fork", "ahpc_pool_append", "ahpc_pool_gather",
     "ahpc_pool_seq_len", "ahpc_pool_seq_pages", "ahpc_pool_free_pages", "ahpc_pool_page_bytes",
@@ -101,6 +102,7 @@ def lib() -> C.CDLL:
     L.ahpc_fa_strides.argtypes = [i32, i64, i64, i64, i64, C.POINTER(C.c_int64 * 4)]
     L.ahpc_fa_fwd.argtypes = [C.POINTER(FaArgs)]
     L.ahpc_fa_select_kernel.argtypes = [C.POINTER(FaArgs)]
+    L.ahpc_fa_read_error_word.argtypes = [i32, pi32]
     L.ahpc_fa_workspace_bytes.argtypes = [i32, i64, i64, i64, i64, i64, i32]
     L.ahpc_fa_workspace_bytes.restype = C.c_size_t
     L.ahpc_pool_create.argtypes = [C.POINTER(vp), C.POINTER(PoolConfig)]

@@ -78,5 +78,6 @@ struct FaLaunch {                 // validated, device-pointer form of ahpc_fa_a
 ahpc_status launch_fa_simt(const FaLaunch& a);     // fa_simt.cu
 ahpc_status launch_fa_tc(const FaLaunch& a);       // fa_tc.cu
 bool fa_tc_supported(const FaLaunch& a, const char** why);
+ahpc_status fa_tc_read_error_word(int device, int* out);   // fa_tc.cu
 
 }  // namespace ahpc

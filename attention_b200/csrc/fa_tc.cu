@@ -1,6 +1,507 @@
-// placeholder
+// FlashAttention forward on the 5th-generation tensor cores (tcgen05, accumulators in TMEM),
+// for FP16 / BF16 inputs with head_dim 64 or 128.
+//
+// It computes what FlashAttention::forward of the reference means to compute
+// (src/algorithms/flash_attention.cpp:68-112, 277-450): per (batch, head), tiles of
+// S = Q K^T, an online softmax with FP32 statistics, and O += P V, skipping key tiles above the
+// causal diagonal (:424) - but both contractions run as tcgen05.mma with operands staged in shared
+// memory by TMA and S / O living in tensor memory.
+//
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles and walks the key tiles
+// once for both.  Roles (320 threads):
+//   warps 0-3   softmax of query tile 0: one thread per row (tcgen05.ld 32x32b gives a thread its
+//               whole row: no shuffles for the row max / sum), writes P back into TMEM over S
+//   warps 4-7   the same for query tile 1
+//   warp  8     lane 0 issues every tcgen05.mma and the commits that signal their completion
+//   warp  9     lane 0 issues the TMA loads (Q tiles once, then K0,V0,K1,V1,... through a ring)
+// While one tile's warps do their softmax, the tensor pipe works on the other tile's MMAs.
+//
+// TMEM (512 columns): S0 | S1 (128 fp32 columns each; P0/P1 alias the first 64 columns of S0/S1
+// as packed 16-bit pairs) | O0 | O1 (head_dim fp32 columns each).
+// The accumulator O is only rescaled when a row's running maximum grew by more than 2^8 since the
+// maximum in use was fixed; until then the stale maximum stays in use, which is exact because the
+// final division uses a row sum accumulated with the same maximum.
+//
+// Every wait in this kernel is bounded: when a barrier does not complete within the limit the
+// waiting thread records a code in a global error word, raises a CTA-wide abort flag, and every
+// role leaves its loop; tensor memory is then released and the kernel returns.
+#include <cuda.h>
+
+#include <cmath>
+#include <map>
+#include <mutex>
+
 #include "common.cuh"
+#include "sm100_ptx.cuh"
+
 namespace ahpc {
-bool fa_tc_supported(const FaLaunch&, const char** why) { if (why) *why = "not built"; return false; }
-ahpc_status launch_fa_tc(const FaLaunch&) { return fail(AHPC_UNSUPPORTED_OPERATION, "not built"); }
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;                    // query rows per tile
+constexpr int BN = 128;                    // keys per tile
+constexpr int TC_THREADS = 320;
+constexpr int MMA_WARP = 8, TMA_WARP = 9;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about two seconds
+constexpr float RESCALE_THRESHOLD = 8.0f;               // in base-2 exponent units
+
+template <int D> struct Cfg {
+    static constexpr int SUBTILES = D / 64;                 // 64-element (128-byte) wide column blocks
+    static constexpr uint32_t TILE_BYTES = BN * D * 2;       // one Q, K or V tile
+    static constexpr uint32_t SUB_BYTES = BN * 128;          // one 128-row x 128-byte swizzled block
+    static constexpr int STAGES = D == 128 ? 4 : 8;          // K/V ring depth (tiles)
+    static constexpr uint32_t SMEM_TILES = (2 + STAGES) * TILE_BYTES;
+    static constexpr uint32_t SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr uint32_t O_COL = 256;                   // first column of O0
+};
+
+struct TcParams {
+    void* out;
+    float* lse;
+    int batch, heads, seq_q, seq_kv;
+    long long os[4];
+    float scale, scale_log2;
+    int causal;
+    int n_pairs;
+    int* error_word;
+};
+
+struct Barriers {        // one uint64 each, in shared memory
+    uint64_t q[2], s[2], p[2], o[2], full[8], empty[8];
+    uint32_t tmem_base;
+    int abort;
+};
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word, int code) {
+    long long t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 127u) == 127u) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(error_word, 0, code);
+                return false;
+            }
+        }
+    }
 }
+
+// Key tiles the 128-row query tile starting at row r0 needs.
+__device__ __forceinline__ int kv_tiles_for(int r0, int seq_q, int seq_kv, int causal) {
+    if (r0 >= seq_q) return 0;
+    int n = (seq_kv + BN - 1) / BN;
+    if (causal) {
+        const int last_row = min(r0 + BM, seq_q) - 1;
+        n = min(n, last_row / BN + 1);
+    }
+    return n;
+}
+
+// 2^x on the special-function unit; -inf gives +0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+template <> __device__ __forceinline__ uint32_t pack2<false>(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+    using C = Cfg<D>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t q_smem = smem_base;
+    const uint32_t ring_smem = smem_base + 2 * C::TILE_BYTES;
+    Barriers* bars = reinterpret_cast<Barriers*>(smem_aligned + C::SMEM_TILES);
+    volatile int* abort_flag = &bars->abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which (pair of query tiles, batch, head): heavy (late) pairs first when causal
+    const int bh_count = p.batch * p.heads;
+    const int pair_slot = blockIdx.x / bh_count, bh = blockIdx.x % bh_count;
+    const int pair = p.causal ? p.n_pairs - 1 - pair_slot : pair_slot;
+    const int b = bh / p.heads, h = bh % p.heads;
+    const int q0 = pair * 2 * BM;
+    const int n_t0 = kv_tiles_for(q0, p.seq_q, p.seq_kv, p.causal);
+    const int n_t1 = kv_tiles_for(q0 + BM, p.seq_q, p.seq_kv, p.causal);
+    const int n_kv = max(n_t0, n_t1);
+
+    if (threadIdx.x == MMA_WARP * 32) {
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(smem_u32(&bars->q[t]), 1);
+            mbar_init(smem_u32(&bars->s[t]), 1);
+            mbar_init(smem_u32(&bars->p[t]), BM);
+            mbar_init(smem_u32(&bars->o[t]), 1);
+        }
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        bars->abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == MMA_WARP) {
+        __syncwarp();
+        tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == TMA_WARP) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            prefetch_tensormap(&map_q);
+            prefetch_tensormap(&map_k);
+            prefetch_tensormap(&map_v);
+            for (int t = 0; t < 2; ++t) {
+                if ((t == 0 ? n_t0 : n_t1) == 0) continue;
+                const uint32_t bar = smem_u32(&bars->q[t]);
+                mbar_expect_tx(bar, C::TILE_BYTES);
+                for (int sub = 0; sub < C::SUBTILES; ++sub)
+                    tma_load_4d(q_smem + t * C::TILE_BYTES + sub * C::SUB_BYTES, &map_q, bar, sub * 64, q0 + t * BM, h, b);
+            }
+            int issued = 0;
+            bool ok = true;
+            for (int idx = 0; idx < 2 * n_kv && ok; ++idx) {
+                const int slot = idx % C::STAGES, round = idx / C::STAGES;
+                if (round > 0) ok = wait_bounded(smem_u32(&bars->empty[slot]), (round - 1) & 1, abort_flag, p.error_word, 100 + slot);
+                if (!ok) break;
+                const uint32_t bar = smem_u32(&bars->full[slot]);
+                mbar_expect_tx(bar, C::TILE_BYTES);
+                const CUtensorMap* map = (idx & 1) ? &map_v : &map_k;
+                for (int sub = 0; sub < C::SUBTILES; ++sub)
+                    tma_load_4d(ring_smem + slot * C::TILE_BYTES + sub * C::SUB_BYTES, map, bar, sub * 64, (idx >> 1) * BN, h, b);
+                issued = idx + 1;
+            }
+            if (!ok) {
+                // Leave no copy in flight: wait (bounded) for the loads of the last ring round issued.
+                for (int idx = max(0, issued - C::STAGES); idx < issued; ++idx) {
+                    const int slot = idx % C::STAGES, round = idx / C::STAGES;
+                    long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&bars->full[slot]), round & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
+                }
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_kv > 0) {
+            constexpr uint32_t IDESC_S = idesc_f16(BF16 ? 1 : 0, BM, BN, 0, 0);     // Q (K-major) x K (K-major)
+            constexpr uint32_t IDESC_O = idesc_f16(BF16 ? 1 : 0, BM, D, 0, 1);      // P (TMEM)    x V (MN-major)
+            const int n_t[2] = {n_t0, n_t1};
+            bool ok = true;
+
+            // S_t = Q_t K_j^T : head_dim/16 MMAs of K = 16
+            auto issue_s = [&](int t, int slot) {
+                const uint32_t qa = q_smem + t * C::TILE_BYTES, ka = ring_smem + slot * C::TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * C::SUB_BYTES + (kk & 3) * 32;
+                    mma_ss(tmem + t * BN, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), IDESC_S, kk > 0);
+                }
+                tc_commit(smem_u32(&bars->s[t]));
+            };
+            // O_t (+)= P_t V_j : 8 MMAs of K = 16 keys; V is MN-major (head_dim contiguous)
+            auto issue_o = [&](int t, int slot, bool first) {
+                const uint32_t va = ring_smem + slot * C::TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    mma_ts(tmem + C::O_COL + t * D, tmem + t * BN + kk * 8, smem_desc_sw128(va + kk * 16 * 128, C::SUB_BYTES, 1024),
+                           IDESC_O, !(first && kk == 0));
+                tc_commit(smem_u32(&bars->o[t]));
+            };
+
+            for (int t = 0; t < 2 && ok; ++t)
+                if (n_t[t] > 0) ok = wait_bounded(smem_u32(&bars->q[t]), 0, abort_flag, p.error_word, 200 + t);
+            if (ok) ok = wait_bounded(smem_u32(&bars->full[0]), 0, abort_flag, p.error_word, 210);
+            if (ok) {
+                tc_fence_after_sync();
+                for (int t = 0; t < 2; ++t)
+                    if (n_t[t] > 0) issue_s(t, 0);
+                tc_commit(smem_u32(&bars->empty[0]));
+            }
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const int idx_v = 2 * j + 1, idx_k = 2 * j + 2;
+                const int slot_v = idx_v % C::STAGES, slot_k = idx_k % C::STAGES;
+                const bool more = j + 1 < n_kv;
+                ok = wait_bounded(smem_u32(&bars->full[slot_v]), (idx_v / C::STAGES) & 1, abort_flag, p.error_word, 220);
+                if (ok && more) ok = wait_bounded(smem_u32(&bars->full[slot_k]), (idx_k / C::STAGES) & 1, abort_flag, p.error_word, 230);
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (j < n_t[t]) {
+                        ok = wait_bounded(smem_u32(&bars->p[t]), j & 1, abort_flag, p.error_word, 240 + t);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_o(t, slot_v, j == 0);
+                    }
+                    if (j + 1 < n_t[t]) issue_s(t, slot_k);
+                }
+                if (ok) {
+                    tc_commit(smem_u32(&bars->empty[slot_v]));
+                    if (more) tc_commit(smem_u32(&bars->empty[slot_k]));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax + epilogue
+        const int t = warp >> 2;                               // query tile of this warpgroup
+        const int n_mine = t == 0 ? n_t0 : n_t1;
+        const int r_in_tile = (warp & 3) * 32 + lane;
+        const int row = q0 + t * BM + r_in_tile;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t s_addr = tmem + lane_base + t * BN;
+        const uint32_t o_addr = tmem + lane_base + C::O_COL + t * D;
+        float m_used = -INFINITY, l_run = 0.f;
+        bool ok = true;
+
+        for (int j = 0; j < n_mine; ++j) {
+            ok = wait_bounded(smem_u32(&bars->s[t]), j & 1, abort_flag, p.error_word, 300 + t);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t sr[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr[c]);
+            tmem_wait_ld();
+
+            const int k0 = j * BN;
+            const bool need_mask = (p.causal && k0 + BN - 1 > q0 + t * BM) || (k0 + BN > p.seq_kv);
+            float row_max = -INFINITY;
+            if (need_mask) {
+                const int limit = p.causal ? min(p.seq_kv - 1, row) : p.seq_kv - 1;     // last visible key
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float x = __uint_as_float(sr[c][i]);
+                        if (k0 + c * 32 + i > limit) x = -INFINITY;
+                        sr[c][i] = __float_as_uint(x);
+                        row_max = fmaxf(row_max, x);
+                    }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) row_max = fmaxf(row_max, __uint_as_float(sr[c][i]));
+            }
+
+            if (j == 0) {
+                m_used = row_max;
+            } else {
+                const bool grow = (row_max - m_used) * p.scale_log2 > RESCALE_THRESHOLD;   // -inf cases: false or inf>thr
+                if (__any_sync(0xffffffffu, grow)) {
+                    // S_t(j) completing implies PV_t(j-1) completed (MMAs retire in issue order): O_t is stable.
+                    const float m_new = fmaxf(m_used, row_max);
+                    const float alpha = (m_used == -INFINITY) ? 0.f : exp2f((m_used - m_new) * p.scale_log2);
+                    l_run *= alpha;
+                    m_used = m_new;
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t orow[32];
+                        tmem_ld32(o_addr + c * 32, orow);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                        tmem_st32(o_addr + c * 32, orow);
+                    }
+                }
+            }
+            const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+            const float neg_m = -m_eff * p.scale_log2;
+            float psum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, neg_m));
+                    psum += p0 + p1;
+                    packed[i] = pack2<BF16>(p0, p1);
+                }
+                tmem_st16(s_addr + c * 16, packed);
+            }
+            l_run += psum;
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars->p[t]));
+        }
+
+        if (ok && n_mine > 0) ok = wait_bounded(smem_u32(&bars->o[t]), (n_mine - 1) & 1, abort_flag, p.error_word, 310 + t);
+        if (ok && n_mine > 0) {
+            tc_fence_after_sync();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            uint16_t* orow_g = static_cast<uint16_t*>(p.out) + b * p.os[0] + h * p.os[1] + (long long)row * p.os[2];
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t orow[32];
+                tmem_ld32(o_addr + c * 32, orow);      // warp-collective: rows past seq_q still take part
+                tmem_wait_ld();
+                if (row < p.seq_q) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 v;
+                        v.x = pack2<BF16>(__uint_as_float(orow[8 * i + 0]) * inv, __uint_as_float(orow[8 * i + 1]) * inv);
+                        v.y = pack2<BF16>(__uint_as_float(orow[8 * i + 2]) * inv, __uint_as_float(orow[8 * i + 3]) * inv);
+                        v.z = pack2<BF16>(__uint_as_float(orow[8 * i + 4]) * inv, __uint_as_float(orow[8 * i + 5]) * inv);
+                        v.w = pack2<BF16>(__uint_as_float(orow[8 * i + 6]) * inv, __uint_as_float(orow[8 * i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow_g + c * 32 + i * 8) = v;
+                    }
+                }
+            }
+            if (p.lse && row < p.seq_q)
+                p.lse[((long long)b * p.heads + h) * p.seq_q + row] =
+                    l_run > 0.f ? m_used * p.scale + logf(l_run) : -INFINITY;
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// 4-d view (dim, position, head, batch) of a [B,H,S,D] tensor with element strides st; box 64 x 128.
+ahpc_status make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D, const int64_t st[4]) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(AHPC_BACKEND_NOT_AVAILABLE, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[0] * 2};
+    const cuuint32_t box[4] = {64, BN, 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, dtype == AHPC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                    const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(AHPC_INVALID_PARAMETERS, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return AHPC_SUCCESS;
+}
+
+struct ErrorWords {
+    std::mutex mu;
+    std::map<int, int*> per_device;
+};
+ErrorWords& error_words() {
+    static ErrorWords e;
+    return e;
+}
+ahpc_status error_word_for(int device, int** out) {
+    ErrorWords& e = error_words();
+    std::lock_guard<std::mutex> lock(e.mu);
+    auto it = e.per_device.find(device);
+    if (it == e.per_device.end()) {
+        int* w = nullptr;
+        AHPC_CUDA_OK(cudaMalloc(&w, sizeof(int)));
+        AHPC_CUDA_OK(cudaMemset(w, 0, sizeof(int)));
+        it = e.per_device.emplace(device, w).first;
+    }
+    *out = it->second;
+    return AHPC_SUCCESS;
+}
+
+bool map_ok(const void* ptr, const int64_t st[4]) {
+    if (reinterpret_cast<uintptr_t>(ptr) % 16) return false;
+    if (st[3] != 1) return false;
+    for (int i = 0; i < 3; ++i)
+        if (st[i] <= 0 || (st[i] * 2) % 16 || st[i] * 2 >= (int64_t(1) << 40)) return false;
+    return true;
+}
+
+template <int D, bool BF16>
+ahpc_status launch(const FaLaunch& a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcParams& p) {
+    using C = Cfg<D>;
+    auto kernel = fa_fwd_tc_kernel<D, BF16>;
+    AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
+    const long long ctas = (long long)p.n_pairs * a.batch * a.heads;
+    kernel<<<(unsigned)ctas, TC_THREADS, C::SMEM_BYTES, a.stream>>>(mq, mk, mv, p);
+    AHPC_CUDA_OK(cudaGetLastError());
+    return AHPC_SUCCESS;
+}
+
+}  // namespace
+
+bool fa_tc_supported(const FaLaunch& a, const char** why) {
+    const char* r = nullptr;
+    if (a.dtype != AHPC_F16 && a.dtype != AHPC_BF16) r = "inputs are not FP16/BF16";
+    else if (a.head_dim != 64 && a.head_dim != 128) r = "head_dim is not 64 or 128";
+    else if (a.mask) r = "an explicit attention mask is given";
+    else if (!(a.scale > 0.f)) r = "softmax scale is not positive";
+    else if (!map_ok(a.q, a.qs) || !map_ok(a.k, a.ks) || !map_ok(a.v, a.vs)) r = "q/k/v are not 16-byte aligned with unit inner stride";
+    else if (a.os[3] != 1 || reinterpret_cast<uintptr_t>(a.out) % 16 || a.os[0] % 8 || a.os[1] % 8 || a.os[2] % 8)
+        r = "out is not 16-byte aligned with unit inner stride";
+    else if ((long long)((a.seq_q + 2 * BM - 1) / (2 * BM)) * a.batch * a.heads > 2147483647ll) r = "grid too large";
+    if (why) *why = r;
+    return r == nullptr;
+}
+
+ahpc_status launch_fa_tc(const FaLaunch& a) {
+    const char* why = nullptr;
+    if (!fa_tc_supported(a, &why)) return fail(AHPC_UNSUPPORTED_OPERATION, "tensor-core kernel not applicable: %s", why);
+    CUtensorMap mq, mk, mv;
+    AHPC_TRY(make_map(&mq, a.q, a.dtype, a.batch, a.heads, a.seq_q, a.head_dim, a.qs));
+    AHPC_TRY(make_map(&mk, a.k, a.dtype, a.batch, a.heads, a.seq_kv, a.head_dim, a.ks));
+    AHPC_TRY(make_map(&mv, a.v, a.dtype, a.batch, a.heads, a.seq_kv, a.head_dim, a.vs));
+    TcParams p;
+    p.out = a.out; p.lse = a.lse;
+    p.batch = a.batch; p.heads = a.heads; p.seq_q = a.seq_q; p.seq_kv = a.seq_kv;
+    for (int i = 0; i < 4; ++i) p.os[i] = a.os[i];
+    p.scale = a.scale;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.causal = a.causal;
+    p.n_pairs = (a.seq_q + 2 * BM - 1) / (2 * BM);
+    AHPC_TRY(error_word_for(a.device, &p.error_word));
+    const bool bf16 = a.dtype == AHPC_BF16;
+    if (a.head_dim == 128) return bf16 ? launch<128, true>(a, mq, mk, mv, p) : launch<128, false>(a, mq, mk, mv, p);
+    return bf16 ? launch<64, true>(a, mq, mk, mv, p) : launch<64, false>(a, mq, mk, mv, p);
+}
+
+// Non-zero when a kernel of this file gave up on a wait since the last call (synchronises the device).
+ahpc_status fa_tc_read_error_word(int device, int* out) {
+    int* w = nullptr;
+    AHPC_TRY(error_word_for(device, &w));
+    AHPC_CUDA_OK(cudaDeviceSynchronize());
+    AHPC_CUDA_OK(cudaMemcpy(out, w, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*out) AHPC_CUDA_OK(cudaMemset(w, 0, sizeof(int)));
+    return AHPC_SUCCESS;
+}
+
+}  // namespace ahpc

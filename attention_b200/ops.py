@@ -73,8 +73,9 @@ def flash_attention_forward(q, k, v, *, causal=False, scale=0.0, mask=None, out=
 def select_kernel(q, k, *, mask=None, kernel=abi.KERNEL_AUTO) -> int:
     """Which kernel the library would run for tensors shaped like these."""
     a = abi.FaArgs()
-    a.q = a.k = a.v = a.out = 1  # only shapes matter here
-    a.mask = 1 if mask is not None else None
+    a.q = a.out = q.data_ptr()   # nothing is read or written: shapes, strides and alignment decide
+    a.k = a.v = k.data_ptr()
+    a.mask = q.data_ptr() if mask is not None else None
     a.dtype = _dtype_code(q)
     a.batch, a.heads, a.seq_q, a.head_dim = q.shape
     a.seq_kv = k.shape[2]

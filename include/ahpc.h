@@ -132,6 +132,12 @@ AHPC_API ahpc_status ahpc_fa_fwd(const ahpc_fa_args* args);
 AHPC_API size_t ahpc_fa_workspace_bytes(int32_t dtype, int64_t batch, int64_t heads, int64_t seq_q,
                                         int64_t seq_kv, int64_t head_dim, int32_t with_mask);
 
+/* Every wait inside the tensor-core kernel is bounded; a wait that gives up records a non-zero
+ * code in a per-device word instead of hanging.  This call synchronises the device, returns the
+ * word in *out and clears it.  0 = no kernel gave up since the last call.  (No counterpart in the
+ * reference, whose kernels have no waits.) */
+AHPC_API ahpc_status ahpc_fa_read_error_word(int32_t device, int32_t* out);
+
 /* Which kernel ahpc_fa_fwd would run for these arguments (AHPC_FA_KERNEL_SIMT or _TC);
  * a negative value means the arguments are invalid. */
 AHPC_API int32_t ahpc_fa_select_kernel(const ahpc_fa_args* args);

@@ -115,3 +115,105 @@ def test_error_statuses_on_gpu():
     with pytest.raises(abi.AhpcError) as e:
         ops.flash_attention_forward(big, big, big)
     assert e.value.status == 6
+
+
+# ---- tensor-core (tcgen05 / TMEM) kernel ----------------------------------------------------------
+
+def _error_word():
+    import ctypes as C
+    w = C.c_int32(-1)
+    abi.check(abi.lib().ahpc_fa_read_error_word(0, C.byref(w)))
+    return w.value
+
+
+@pytest.mark.parametrize("S", [1, 17, 128, 129, 255, 256, 257, 640, 1000])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype,D", [("bf16", 128), ("f16", 64)])
+def test_tc_sequence_lengths(S, causal, dtype, D):
+    run_case(2, 3, S, S, D, dtype, causal, 500 + S, kernel=abi.KERNEL_TC)
+    assert _error_word() == 0
+
+
+@pytest.mark.parametrize("dtype,D", [("f16", 128), ("bf16", 64)])
+def test_tc_rectangular(dtype, D):
+    run_case(1, 2, 300, 700, D, dtype, False, 31, kernel=abi.KERNEL_TC)
+    run_case(1, 2, 700, 300, D, dtype, True, 32, kernel=abi.KERNEL_TC)
+    assert _error_word() == 0
+
+
+def test_tc_is_the_default_for_16bit_and_bshd_views_work():
+    t = torch.zeros((1, 2, 64, 128), dtype=torch.bfloat16, device=DEV)
+    assert ops.select_kernel(t, t) == abi.KERNEL_TC
+    assert ops.select_kernel(t.float(), t.float()) == abi.KERNEL_SIMT
+    assert ops.select_kernel(t, t, mask=True) == abi.KERNEL_SIMT
+    run_case(2, 4, 300, 300, 128, "bf16", True, 33, layout="BSHD", kernel=abi.KERNEL_TC)
+    run_case(2, 4, 300, 300, 64, "f16", False, 34, host=True)
+    assert _error_word() == 0
+
+
+def test_tc_large_scores_exercise_the_lazy_rescale():
+    """Inputs scaled so that row maxima keep growing along the keys: the accumulator rescale path runs."""
+    B, H, S, D = 1, 2, 1024, 128
+    rng = np.random.default_rng(77)
+    ramp = np.linspace(0.2, 6.0, S, dtype=np.float32)[None, None, :, None]
+    q = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32) * 2, "bf16"), "bf16")
+    k = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32) * ramp, "bf16"), "bf16")
+    v = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32), "bf16"), "bf16")
+    want = o.attention_fwd(q, k, v, 1 / np.sqrt(D), False)
+    tq, tk, tv = (torch.from_numpy(x).to(torch.bfloat16).to(DEV) for x in (q, k, v))
+    out = ops.flash_attention_forward(tq, tk, tv, scale=1 / np.sqrt(D), kernel=abi.KERNEL_TC)
+    u.assert_close(u.torch_to_f32(out), want, "bf16", "growing maxima")
+    assert _error_word() == 0
+
+
+def test_tc_lse():
+    B, H, S, D = 1, 2, 300, 64
+    (q, k, v), (tq, tk, tv) = u.rounded_inputs((B, H, S, D), "f16", 41)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=DEV)
+    ops.flash_attention_forward(tq.to(DEV), tk.to(DEV), tv.to(DEV), causal=True, lse=lse, kernel=abi.KERNEL_TC)
+    _, want = o.attention_fwd(q, k, v, 1 / np.sqrt(D), True, return_lse=True)
+    assert np.abs(lse.cpu().numpy() - want).max() <= 2e-3
+
+
+def _full_size_inputs(c):
+    g = torch.Generator(device=DEV).manual_seed(c.seed)
+    shape = (c.batch, c.heads, c.seq, c.head_dim)
+    return [(torch.randn(shape, generator=g, device=DEV, dtype=torch.float32) * c.input_scale).to(torch.bfloat16) for _ in range(3)]
+
+
+def _check_rows(c, tq, tk, tv, out, b, h, r0, r1):
+    """Oracle on query rows [r0, r1) of one (b, h) at full key length, causal by an explicit mask."""
+    q = tq[b, h, r0:r1].float().cpu().numpy()[None, None]
+    k = tk[b, h].float().cpu().numpy()[None, None]
+    v = tv[b, h].float().cpu().numpy()[None, None]
+    rows = np.arange(r0, r1)[:, None]
+    mask = (np.arange(c.seq)[None, :] <= rows).astype(np.float32)[None] if c.causal else None
+    want = o.attention_fwd(q, k, v, 1 / np.sqrt(c.head_dim), False, mask)
+    u.assert_close(u.torch_to_f32(out[b, h, r0:r1])[None, None], want, "bf16", f"{c.name} b{b} h{h} rows {r0}:{r1}")
+
+
+def test_c2_full_size_sampled_against_oracle_and_constant_v_property():
+    """Configuration 2 in full (BF16 causal B4 S4096 H32 D128, N(0,1)*0.5): the oracle checks whole
+    (batch, head) pairs; a constant V must come back as that constant everywhere."""
+    c = synth.C2
+    tq, tk, tv = _full_size_inputs(c)
+    out = ops.flash_attention_forward(tq, tk, tv, causal=True)
+    assert ops.select_kernel(tq, tk) == abi.KERNEL_TC
+    for b, h in [(0, 0), (3, 31), (1, 17)]:
+        _check_rows(c, tq, tk, tv, out, b, h, 0, c.seq)
+    vc = torch.full_like(tv, 0.75)
+    out2 = ops.flash_attention_forward(tq, tk, vc, causal=True)
+    assert float((out2.float() - 0.75).abs().max()) <= 4e-3
+    assert _error_word() == 0
+
+
+def test_c4_full_size_sampled_row_blocks():
+    """Configuration 4 in full (BF16 causal B1 S32768 H16 D128, N(0,1)): first, diagonal-crossing and
+    last row blocks of two heads against the oracle."""
+    c = synth.C4
+    tq, tk, tv = _full_size_inputs(c)
+    out = ops.flash_attention_forward(tq, tk, tv, causal=True)
+    for h in (0, 15):
+        for r0 in (0, 16320, c.seq - 128):
+            _check_rows(c, tq, tk, tv, out, 0, h, r0, r0 + 128)
+    assert _error_word() == 0
