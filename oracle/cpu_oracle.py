@@ -25,6 +25,7 @@ def _lib(native: bool = False) -> C.CDLL:
         lib = C.CDLL(_b.build_oracle(native=native))
         lib.oracle_attention_fwd.argtypes = [_F, _F, _F, _F, _F] + [C.c_int64] * 5 + [_I64] * 4 + [C.c_float, C.c_int, _F]
         lib.oracle_attention_fwd_f32acc.argtypes = [_F, _F, _F, _F] + [C.c_int64] * 4 + [C.c_float, C.c_int, C.c_int]
+        lib.oracle_attention_fwd_f32acc_rows.argtypes = [_F, _F, _F, _F] + [C.c_int64] * 4 + [C.c_float, C.c_int, C.c_int, C.c_int64, C.c_int64]
         lib.oracle_paged_decode.argtypes = [_F, _F, _F, _F, _I32, _I32] + [C.c_int64] * 5 + [C.c_float]
         lib.oracle_paged_decode_f32acc.argtypes = [_F, C.c_void_p, C.c_void_p, _F, _I32, _I32] + [C.c_int64] * 5 + [C.c_float, C.c_int, C.c_int]
         lib.oracle_convert_to_f32.argtypes = [C.c_void_p, _F, C.c_int64, C.c_int]
@@ -98,13 +99,17 @@ def attention_fwd(q, k, v, scale: float, causal: bool = False, mask=None, return
     return (out, lse) if return_lse else out
 
 
-def attention_fwd_f32acc(q, k, v, scale: float, causal: bool, threads: int = 0, native: bool = False):
-    """The float-accumulating port (contiguous [B,H,S,D]); this is what the CPU baseline times."""
+def attention_fwd_f32acc(q, k, v, scale: float, causal: bool, threads: int = 0, native: bool = False,
+                         rows: tuple[int, int] | None = None, out=None):
+    """The float-accumulating port (contiguous [B,H,S,D]); this is what the CPU baseline times.
+    rows=(begin, end) computes only those query rows of every (b,h)."""
     q, k, v = (np.ascontiguousarray(x, dtype=np.float32) for x in (q, k, v))
     B, H, S, D = q.shape
-    out = np.empty_like(q)
-    _lib(native).oracle_attention_fwd_f32acc(_fp(q), _fp(k), _fp(v), _fp(out), B, H, S, D,
-                                             float(scale), int(causal), int(threads))
+    if out is None:
+        out = np.zeros_like(q)
+    r0, r1 = rows if rows is not None else (0, S)
+    _lib(native).oracle_attention_fwd_f32acc_rows(_fp(q), _fp(k), _fp(v), _fp(out), B, H, S, D,
+                                                  float(scale), int(causal), int(threads), r0, r1)
     return out
 
 

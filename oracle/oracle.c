@@ -160,11 +160,14 @@ ORACLE_API void oracle_attention_fwd(
 
 /*
  * The same loop nest as the reference's test helper, float accumulation, contiguous
- * [B,H,S,D] buffers, parallel over (b,h).  This is the "port" timed as the CPU baseline.
+ * [B,H,S,D] buffers, parallel over (b,h) and query rows.  This is the "port" timed as the CPU
+ * baseline.  Only query rows [row_begin, row_end) of every (b,h) are computed (rows outside are
+ * left untouched), so that a bounded sample of a large configuration can be timed.
  */
-ORACLE_API void oracle_attention_fwd_f32acc(
+ORACLE_API void oracle_attention_fwd_f32acc_rows(
     const float* q, const float* k, const float* v, float* out,
-    int64_t B, int64_t H, int64_t S, int64_t D, float scale, int causal, int num_threads)
+    int64_t B, int64_t H, int64_t S, int64_t D, float scale, int causal, int num_threads,
+    int64_t row_begin, int64_t row_end)
 {
 #ifdef _OPENMP
     if (num_threads > 0) omp_set_num_threads(num_threads);
@@ -174,7 +177,7 @@ ORACLE_API void oracle_attention_fwd_f32acc(
         float* w = (float*)malloc(sizeof(float) * (size_t)S);
         #pragma omp for collapse(2) schedule(dynamic, 8)
         for (int64_t bh = 0; bh < B * H; ++bh) {
-            for (int64_t i = 0; i < S; ++i) {
+            for (int64_t i = row_begin; i < row_end; ++i) {
                 const float* qb = q + bh * S * D; const float* kb = k + bh * S * D;
                 const float* vb = v + bh * S * D; float* ob = out + bh * S * D;
                 int64_t n = causal ? i + 1 : S;
@@ -197,6 +200,13 @@ ORACLE_API void oracle_attention_fwd_f32acc(
         }
         free(w);
     }
+}
+
+ORACLE_API void oracle_attention_fwd_f32acc(
+    const float* q, const float* k, const float* v, float* out,
+    int64_t B, int64_t H, int64_t S, int64_t D, float scale, int causal, int num_threads)
+{
+    oracle_attention_fwd_f32acc_rows(q, k, v, out, B, H, S, D, scale, causal, num_threads, 0, S);
 }
 
 /* ---------------------------------------------------------------- paged decode */
