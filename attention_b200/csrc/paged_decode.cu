@@ -18,6 +18,7 @@
 #include <cstdlib>
 
 #include <algorithm>
+#include <mutex>
 
 #include "pool.cuh"
 
@@ -348,6 +349,37 @@ ahpc_status launch_decode_q(const ahpc_pool* pool, const DecodeParams& dp, int q
     return fail(AHPC_INVALID_PARAMETERS, "unknown q/out dtype %d", qo_dtype);
 }
 
+
+// ---- decode without any allocation ----------------------------------------------------------------
+// Split-KV scratch that belongs to the library image instead of the heap: every GPU that loads the
+// library carries these bytes from module load until the process exits.
+constexpr size_t STATIC_SCRATCH_BYTES = AHPC_PAGED_DECODE_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_decode_scratch[STATIC_SCRATCH_BYTES];
+
+// In host code `g_static_decode_scratch` is only a handle for the symbol, not an address a kernel
+// can use; the device address has to be asked for, per device, with that device current.
+constexpr int MAX_STATIC_DEVICES = 64;
+unsigned char* g_static_scratch_addr[MAX_STATIC_DEVICES] = {};
+std::mutex g_static_scratch_mu;
+
+ahpc_status static_scratch_for(int device, unsigned char** out) {
+    if (device < 0 || device >= MAX_STATIC_DEVICES)
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: device %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (!g_static_scratch_addr[device]) {
+        void* ptr = nullptr;                                // the caller made `device` current
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_decode_scratch);
+        if (e != cudaSuccess || !ptr) {
+            (void)cudaGetLastError();
+            return fail(AHPC_COMPUTATION_FAILED, "ahpc_paged_decode_static: cudaGetSymbolAddress failed on device %d: %s",
+                        device, cudaGetErrorString(e));
+        }
+        g_static_scratch_addr[device] = static_cast<unsigned char*>(ptr);
+    }
+    *out = g_static_scratch_addr[device];
+    return AHPC_SUCCESS;
+}
+
 }  // namespace
 }  // namespace ahpc
 
@@ -429,6 +461,62 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
     if (host_o) AHPC_CUDA_OK(cudaMemcpyAsync(a->out, dout, qo_bytes, cudaMemcpyDeviceToHost, st));
     if (host_q || host_o) AHPC_CUDA_OK(cudaStreamSynchronize(st));
     return AHPC_SUCCESS;
+}
+
+size_t ahpc_paged_decode_static_capacity(void) { return STATIC_SCRATCH_BYTES; }
+
+ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* a) {
+    if (!a || !a->pool) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode_static: NULL argument");
+    ahpc_pool* p = a->pool;
+    if (a->n_seqs <= 0) return AHPC_SUCCESS;
+    if (!a->seqs || !a->q || !a->out) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode_static: seqs, q and out must not be NULL");
+    if (!dtype_valid(a->qo_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: unknown dtype %d", a->qo_dtype);
+    if (a->n_seqs > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode_static: at most 65535 sequences per call");
+    if (p->cfg.heads > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode_static: at most 65535 heads");
+    // Host tensors would need a staging buffer, i.e. an allocation: this entry point takes device memory only.
+    if (is_host_pointer(a->q) || is_host_pointer(a->out))
+        return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode_static: q and out must be device pointers (staging host tensors would allocate)");
+    std::lock_guard<std::mutex> lock(p->mu);
+    AHPC_TRY(use_device(p->cfg.device));
+    cudaStream_t st = (cudaStream_t)a->stream;
+    int max_len = 0;
+    for (int i = 0; i < a->n_seqs; ++i) {
+        const int s = a->seqs[i];
+        if (s < 0 || s >= p->cfg.max_seqs || !p->h_live[s]) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode_static: sequence %d not found", s);
+        max_len = std::max(max_len, p->h_len[s]);
+    }
+    const int ps = p->cfg.page_size;
+    const int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device));
+    if (split % ps) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: split_tokens %d is not a multiple of the page size %d", split, ps);
+    if (!fast_path(p) && split > GEN_MAX_SPLIT)
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: split_tokens %d exceeds %d for this pool configuration", split, GEN_MAX_SPLIT);
+    const int max_chunks = std::max(1, (max_len + split - 1) / split);
+    const ScratchLayout lay = scratch_layout(a->n_seqs, max_chunks, p->cfg.heads, p->cfg.head_dim);
+    if (lay.total > STATIC_SCRATCH_BYTES)
+        return fail(AHPC_MEMORY_ALLOCATION_FAILED,
+                    "ahpc_paged_decode_static: %d sequences x %d chunks of %d tokens need %zu bytes of split-KV scratch, the built-in "
+                    "buffer holds %zu; pass fewer sequences per call or a larger split_tokens, or use ahpc_paged_decode",
+                    a->n_seqs, max_chunks, split, lay.total, STATIC_SCRATCH_BYTES);
+    unsigned char* sc = nullptr;
+    AHPC_TRY(static_scratch_for(p->cfg.device, &sc));
+    // Nothing in the scratch has to start at zero: every partial a combine reads was written by this
+    // call's decode kernel first; leftovers of earlier calls are never read.
+    AHPC_CUDA_OK(cudaMemcpyAsync(sc + lay.seqs_off, a->seqs, (size_t)a->n_seqs * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+
+    DecodeParams dp;
+    dp.q = a->q; dp.out = a->out; dp.k_data = p->k_data; dp.v_data = p->v_data;
+    dp.table = p->table; dp.seq_len = p->seq_len;
+    dp.seqs = reinterpret_cast<const int32_t*>(sc + lay.seqs_off);
+    dp.part_ml = reinterpret_cast<float2*>(sc + lay.ml_off);
+    dp.part_o = reinterpret_cast<float*>(sc + lay.o_off);
+    dp.n_seqs = a->n_seqs; dp.heads = p->cfg.heads; dp.head_dim = p->cfg.head_dim; dp.page_size = ps;
+    dp.max_pages = p->cfg.max_pages_per_seq; dp.max_chunks = max_chunks; dp.split = split;
+    dp.page_elems = p->page_elems;
+    const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);
+    dp.scale_log2 = scale * LOG2E;
+    if (p->cfg.dtype == AHPC_F32) return launch_decode_q<float>(p, dp, a->qo_dtype, st);
+    if (p->cfg.dtype == AHPC_F16) return launch_decode_q<__half>(p, dp, a->qo_dtype, st);
+    return launch_decode_q<__nv_bfloat16>(p, dp, a->qo_dtype, st);
 }
 
 }  // extern "C"

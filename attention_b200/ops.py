@@ -200,8 +200,9 @@ class KVPool:
         abi.check(abi.lib().ahpc_pool_read_error_flag(self._p, C.byref(f), self._stream()))
         return f.value
 
-    def decode(self, seqs, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, split_tokens=0):
-        """q: [n_seqs, heads, head_dim]; returns out of the same shape and dtype."""
+    def decode(self, seqs, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, split_tokens=0, no_alloc=False):
+        """q: [n_seqs, heads, head_dim]; returns out of the same shape and dtype.  no_alloc=True goes
+        through ahpc_paged_decode_static (fixed built-in scratch, device tensors only)."""
         seqs = _i32(seqs)
         assert q.is_contiguous() and tuple(q.shape) == (seqs.size, self.heads, self.head_dim)
         if out is None:
@@ -211,5 +212,6 @@ class KVPool:
         a.pool, a.seqs, a.n_seqs = self._p, _pi32(seqs), seqs.size
         a.q, a.out, a.qo_dtype = q.data_ptr(), out.data_ptr(), _dtype_code(q)
         a.scale, a.split_tokens, a.stream = float(scale), int(split_tokens), self._stream()
-        abi.check(abi.lib().ahpc_paged_decode(C.byref(a)))
+        fn = abi.lib().ahpc_paged_decode_static if no_alloc else abi.lib().ahpc_paged_decode
+        abi.check(fn(C.byref(a)))
         return out

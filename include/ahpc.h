@@ -239,6 +239,36 @@ AHPC_API ahpc_status ahpc_paged_decode(const ahpc_decode_args* args);
 AHPC_API size_t ahpc_paged_decode_scratch_bytes(const ahpc_pool* pool, int32_t n_seqs, int32_t max_len,
                                                 int32_t split_tokens);
 
+/* The same decode for callers that must not allocate device memory.
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits - inside a serving loop that has
+ * handed all device memory to its own arena and forbids driver allocations afterwards (an
+ * allocation there can fail or stall every stream of the process), or inside a region the host
+ * framework declares allocation-free.  ahpc_paged_decode grows a per-pool scratch buffer with
+ * cudaMalloc whenever a call needs more split-KV partials than the last one did; this entry point
+ * never does.  Its split-KV scratch is a fixed array that is part of the library image:
+ * AHPC_PAGED_DECODE_STATIC_SCRATCH_BYTES on every GPU that loads the library, held until the
+ * process exits.  It calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Differences from ahpc_paged_decode:
+ *   - q and out must be device pointers (host tensors would need a staging buffer); `seqs` is
+ *     still a host array and is copied into the fixed array with cudaMemcpyAsync.
+ *   - A call whose partials do not fit (roughly n_seqs * ceil(max_len / split) * heads *
+ *     (head_dim + 2) * 4 bytes) is refused with MEMORY_ALLOCATION_FAILED and a message naming the
+ *     sizes; nothing is launched.  Pass fewer sequences per call or a larger split_tokens.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress with
+ *     that device current).  Make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the last call left in it.
+ *     Nothing in it needs clearing between calls (a call only reads partials it wrote itself), but
+ *     two calls that overlap on the GPU - different streams, or different pools on one device -
+ *     overwrite each other's partials: serialise them.
+ * The result is the same as ahpc_paged_decode's for the same arguments.
+ * This entry point has no counterpart in the reference. */
+#define AHPC_PAGED_DECODE_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+AHPC_API ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* args);
+/* Size of the fixed scratch array in bytes (= AHPC_PAGED_DECODE_STATIC_SCRATCH_BYTES of the build). */
+AHPC_API size_t ahpc_paged_decode_static_capacity(void);
+
 /* ------------------------------------------------------------------------------------------
  * Multi-GPU partitioning (host arithmetic only; no communication)
  * The (batch, head) pairs of a FlashAttention call, or the heads of a decode pool, are split
