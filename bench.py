@@ -43,7 +43,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (None until a capture exists for that kernel).
-NCU_TRAFFIC = {"fa_fwd_tc_kernel": None, "paged_decode_kernel": None}
+# FA: 165 MB per launch on a quarter of C2 (profiles/fa_fwd_tc_kernel_c2small.md), scaled by the units processed.
+# Decode: read+write = 1.0057 x the algorithmic bytes (profiles/paged_decode_kernel_c3small.md).
+NCU_TRAFFIC = {"fa_fwd_tc_kernel_bytes_per_bh_pair_s4096": 165.3e6 / 32, "paged_decode_kernel_ratio": 1.0057}
 
 
 def load_peaks():
@@ -249,6 +251,10 @@ def bench_fa(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind):
     tflops_total = flops * world / (ms_per_step * 1e-3) / 1e12
     tflops_rank = flops / (ms_per_step * 1e-3) / 1e12
 
+    if args.profile_small:
+        return {"value": tflops_total, "ms_per_step": ms_per_step, "e2e": None, "clocks": clk.summary(), "gpu_launches": args.steps,
+                "roofline": {"bound": "tensor", "achieved": tflops_rank, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                             "frac": tflops_rank / peaks["bf16_tflops"], "traffic": None, "flops_per_launch": flops}}
     # end to end: pinned host tensors through the C ABI; H2D + kernel + D2H inside every step
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     hout = torch.empty_like(hq).pin_memory()
@@ -265,7 +271,8 @@ def bench_fa(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind):
         "e2e": {"value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOPS", "h2d_bytes_per_step": 3 * nbytes,
                 "d2h_bytes_per_step": nbytes, "ms_per_step": ms_e2e},
         "roofline": {"bound": "tensor", "achieved": tflops_rank, "peak": peak, "unit": "TFLOP/s", "frac": tflops_rank / peak,
-                     "traffic": NCU_TRAFFIC["fa_fwd_tc_kernel"], "peak_source": peak_kind + (" burst" if ms < 1000.0 else " sustained"),
+                     "traffic": (NCU_TRAFFIC["fa_fwd_tc_kernel_bytes_per_bh_pair_s4096"] * cfg.batch * cfg.heads if cfg.seq == 4096 else None),
+                     "peak_source": peak_kind + (" burst" if ms < 1000.0 else " sustained"),
                      "frac_of_nominal_2250": tflops_rank / 2250.0, "kernel": "fa_fwd_tc_kernel",
                      "flops_per_launch": flops},
         "clocks": clk.summary(), "gpu_launches": args.steps,
@@ -318,7 +325,7 @@ def bench_decode(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind
     def step_e2e():
         pool.decode(seqs, hq, hout)
 
-    ms_e2e = timed_steps(torch, dist, step_e2e, args.steps, args.warmup) / args.steps
+    ms_e2e = ms_per_step if args.profile_small else timed_steps(torch, dist, step_e2e, args.steps, args.warmup) / args.steps
     sec = ms_per_step * 1e-3
     gbs_rank = by["total_unique"] / sec / 1e9
     res = {
@@ -332,7 +339,7 @@ def bench_decode(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind
         "e2e": {"value": by["total_unique"] * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "tokens_per_s": len(seqs) * world / (ms_e2e * 1e-3),
                 "h2d_bytes_per_step": q.numel() * 2 + len(seqs) * 4, "d2h_bytes_per_step": q.numel() * 2, "ms_per_step": ms_e2e},
         "roofline": {"bound": "hbm", "achieved": gbs_rank, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs_rank / peaks["hbm_gbs"],
-                     "traffic": NCU_TRAFFIC["paged_decode_kernel"], "peak_source": peak_kind, "frac_of_nominal_8000": gbs_rank / 8000.0,
+                     "traffic": NCU_TRAFFIC["paged_decode_kernel_ratio"] * by["total_unique"], "peak_source": peak_kind, "frac_of_nominal_8000": gbs_rank / 8000.0,
                      "kernel": "paged_decode_kernel (+ paged_combine_kernel in the same timed step)",
                      "bytes_per_launch": by["total_unique"]},
         "clocks": clk.summary(), "gpu_launches": 2 * args.steps,
@@ -375,11 +382,20 @@ def main():
     ap.add_argument("--workload", choices=["fa_c2", "fa_c4"], default="fa_c2")
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode section")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-small", action="store_true",
+                    help="reduced copies of the workloads for profiler captures: FA B=2 H=16 S=4096 D=128 causal BF16, "
+                         "decode = the first 16 sequences of C3; no end-to-end or CPU legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     from attention_b200 import synth
     cfg = synth.C2 if args.workload == "fa_c2" else synth.C4
+    dec_cfg = synth.C3
+    if args.profile_small:
+        import dataclasses
+        cfg = dataclasses.replace(synth.C2, name="C2-small", batch=2, heads=16)
+        dec_cfg = dataclasses.replace(synth.C3, name="C3-small", batch=16)
+        args.no_cpu_baseline = True
     if args.impl == "reference":
         run_reference(args, cfg)
         return
@@ -402,7 +418,7 @@ def main():
     torch.cuda.empty_cache()
     dec = None
     if not args.no_decode:
-        dec = bench_decode(torch, dist, synth.C3, args, rank, world, peaks, peak_kind)
+        dec = bench_decode(torch, dist, dec_cfg, args, rank, world, peaks, peak_kind)
 
     if rank == 0:
         line = {
@@ -411,7 +427,8 @@ def main():
             "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
             "config": {"workload": workload_name(cfg), "per_gpu_batch": cfg.batch, "global_batch": cfg.batch * world,
                        "partition": "(batch, head) ranges per GPU, no collective",
-                       "l2": "inputs (512 MB per step) exceed the 126 MB L2; no explicit flush"},
+                       "l2": f"inputs + output of a step ({4 * cfg.batch * cfg.heads * cfg.seq * cfg.head_dim * 2 / 1e6:.0f} MB) "
+                             "exceed the 126 MB L2; no explicit flush"},
             "e2e": fa["e2e"], "roofline": fa["roofline"], "clocks": fa["clocks"], "gpu_launches": fa["gpu_launches"],
         }
         if not args.no_cpu_baseline:
@@ -419,7 +436,7 @@ def main():
             line["cpu_baseline"] = {"value": tflops, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample}
         if dec is not None:
             if not args.no_cpu_baseline:
-                gbs, tps, sample, threads = cpu_decode_baseline(synth.C3, budget_s=10.0)
+                gbs, tps, sample, threads = cpu_decode_baseline(dec_cfg, budget_s=10.0)
                 dec["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "tokens_per_s": tps, "cores": threads, "kind": "port", "sample": sample}
             line["paged_decode"] = dec
             line["gpu_launches"] += dec["gpu_launches"]
