@@ -157,6 +157,14 @@ ahpc_status ahpc_get_device_info(int32_t device, ahpc_device_info* out) {
     return AHPC_SUCCESS;
 }
 
+ahpc_status ahpc_stream_synchronize(int32_t device, void* stream) {
+    AHPC_TRY(use_device(device));
+    AHPC_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return AHPC_SUCCESS;
+}
+
+int32_t ahpc_pointer_is_host(const void* ptr) { return is_host_pointer(ptr) ? 1 : 0; }
+
 ahpc_status ahpc_fa_strides(int32_t layout, int64_t batch, int64_t heads, int64_t seq, int64_t head_dim,
                             int64_t strides[4]) {
     if (!strides) return fail(AHPC_INVALID_INPUT, "ahpc_fa_strides: strides is NULL");

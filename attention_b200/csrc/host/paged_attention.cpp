@@ -1,0 +1,351 @@
+// attention_hpc::PagedAttention: sequence bookkeeping and error behaviour of the reference's class
+// (src/algorithms/paged_attention.cpp:98-130, 333-594) over the device page pool of ahpc.h.
+#include "algorithms/paged_attention.hpp"
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+
+#include "ahpc.h"
+
+namespace attention_hpc {
+
+namespace {
+[[noreturn]] void raise(ahpc_status s) { throw AttentionException(static_cast<AttentionError>(s), ahpc_last_error_string()); }
+void check(ahpc_status s) { if (s) raise(s); }
+size_t dtype_bytes(DataType t) { return t == DataType::FLOAT32 ? 4 : 2; }
+}  // namespace
+
+PagedAttention::PagedAttention() = default;
+
+PagedAttention::~PagedAttention() { destroy_pool(); }
+
+void PagedAttention::destroy_pool() {
+    if (pool_) ahpc_pool_destroy(pool_);
+    pool_ = nullptr;
+    sequences_.clear();
+}
+
+void PagedAttention::create_pool() {
+    destroy_pool();
+    const AttentionParams& p = current_params_;
+    const size_t page_tokens = paged_config_.page_size ? paged_config_.page_size : p.page_size;
+    const size_t page_bytes = 2 * page_tokens * p.num_heads * p.head_dimension * dtype_bytes(paged_config_.kv_cache_dtype);
+    size_t pages = std::max(paged_config_.initial_page_pool_size, paged_config_.memory_pool_size / std::max<size_t>(1, page_bytes));
+    pages = std::min<size_t>(std::max<size_t>(pages, 1), 0x7fffffff);
+    ahpc_pool_config cfg{};
+    cfg.device = device_;
+    cfg.dtype = static_cast<int32_t>(paged_config_.kv_cache_dtype);
+    cfg.num_pages = static_cast<int32_t>(pages);
+    cfg.page_size = static_cast<int32_t>(page_tokens);
+    cfg.heads = static_cast<int32_t>(p.num_heads);
+    cfg.head_dim = static_cast<int32_t>(p.head_dimension);
+    cfg.max_seqs = static_cast<int32_t>(std::max<size_t>(1, paged_config_.max_concurrent_sequences));
+    cfg.max_pages_per_seq = static_cast<int32_t>(std::max<size_t>(1, paged_config_.max_pages_per_sequence));
+    cfg.free_order = nullptr;
+    check(ahpc_pool_create(&pool_, &cfg));
+}
+
+void PagedAttention::configure(const AttentionParams& params, const PerformanceConfig& perf_config) {
+    current_params_ = params;
+    current_perf_config_ = perf_config;
+    if (params.batch_size == 0 || params.sequence_length == 0 || params.num_heads == 0 || params.head_dimension == 0)
+        throw AttentionException(AttentionError::INVALID_PARAMETERS, "Invalid attention parameters: dimensions must be positive");
+    if (params.key_value_heads != 0 && params.key_value_heads != params.num_heads)
+        throw AttentionException(AttentionError::UNSUPPORTED_OPERATION, "key_value_heads != num_heads (grouped-query attention) is not supported");
+    if (params.page_size != 0 && paged_config_.page_size == PagedAttentionConfig{}.page_size) paged_config_.page_size = params.page_size;
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    create_pool();
+    profiling_enabled_ = profiling_enabled_ || perf_config.enable_profiling;
+    is_configured_ = true;
+}
+
+void PagedAttention::configure_paged_attention(const PagedAttentionConfig& paged_config) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    paged_config_ = paged_config;
+    if (is_configured_) create_pool();      // as the reference: a new pool, existing sequences are gone
+}
+
+void PagedAttention::forward(const TensorShape& query_shape, const void* query_data, const TensorShape& key_shape, const void* key_data,
+                             const TensorShape& value_shape, const void* value_data, const TensorShape& output_shape, void* output_data,
+                             const void* attention_mask) {
+    if (!is_configured_)
+        throw AttentionException(AttentionError::INVALID_PARAMETERS, "PagedAttention not configured. Call configure() first.");
+    const auto t0 = std::chrono::steady_clock::now();
+    for (const TensorShape* s : {&query_shape, &key_shape, &value_shape, &output_shape})
+        if (s->dimensions.size() != 4) throw AttentionException(AttentionError::INVALID_INPUT, "tensor shapes must have 4 dimensions {B,S,H,D}");
+    if (!query_data || !key_data || !value_data || !output_data)
+        throw AttentionException(AttentionError::INVALID_INPUT, "Null tensor data pointer");
+    const auto& qd = query_shape.dimensions;
+    const auto& kd = key_shape.dimensions;
+    if (kd[0] != qd[0] || kd[2] != qd[2] || kd[3] != qd[3] || value_shape.dimensions != kd || output_shape.dimensions != qd)
+        throw AttentionException(AttentionError::INVALID_INPUT, "query/key/value/output shapes do not agree");
+    // All query tokens against the whole K/V: the result the temporary-sequence path of the reference
+    // means to produce, computed by the dense forward kernel without a detour through pages.
+    ahpc_fa_args a{};
+    a.q = query_data; a.k = key_data; a.v = value_data; a.out = output_data;
+    a.mask = static_cast<const float*>(attention_mask);
+    a.dtype = static_cast<int32_t>(query_shape.data_type);
+    a.batch = static_cast<int32_t>(qd[0]); a.seq_q = static_cast<int32_t>(qd[1]);
+    a.heads = static_cast<int32_t>(qd[2]); a.head_dim = static_cast<int32_t>(qd[3]);
+    a.seq_kv = static_cast<int32_t>(kd[1]);
+    ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.heads, a.seq_q, a.head_dim, a.q_strides);
+    ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.heads, a.seq_kv, a.head_dim, a.k_strides);
+    ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.heads, a.seq_kv, a.head_dim, a.v_strides);
+    ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.heads, a.seq_q, a.head_dim, a.o_strides);
+    a.scale = current_params_.scale_factor;
+    a.causal = current_params_.causal_mask ? 1 : 0;
+    a.device = device_;
+    a.stream = stream_;
+    check(ahpc_fa_fwd(&a));
+    if (profiling_enabled_) {
+        check(ahpc_stream_synchronize(device_, stream_));
+        profiling_results_.emplace_back("forward_pass", std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
+    }
+}
+
+void PagedAttention::backward(const TensorShape&, const void*, const TensorShape&, const void*, const TensorShape&, const void*,
+                              const TensorShape&, const void*, const TensorShape&, void*, const TensorShape&, void*,
+                              const TensorShape&, void*, const void*) {
+    throw AttentionException(AttentionError::UNSUPPORTED_OPERATION, "backward pass is not part of this library (forward inference paths only)");
+}
+
+size_t PagedAttention::get_workspace_size(const AttentionParams& p) const {
+    const size_t page_tokens = paged_config_.page_size;
+    const size_t pages = (p.sequence_length + page_tokens - 1) / page_tokens;
+    return pages * 2 * page_tokens * p.num_heads * p.head_dimension * dtype_bytes(paged_config_.kv_cache_dtype) * p.batch_size;
+}
+
+void PagedAttention::set_workspace(void* workspace_ptr, size_t workspace_size) {
+    workspace_ptr_ = workspace_ptr;
+    workspace_size_ = workspace_size;
+}
+
+bool PagedAttention::supports_data_type(DataType t) const { return t == DataType::FLOAT32 || t == DataType::FLOAT16 || t == DataType::BFLOAT16; }
+bool PagedAttention::supports_memory_layout(MemoryLayout layout) const { return layout == MemoryLayout::ROW_MAJOR; }
+std::string PagedAttention::get_backend_name() const { return "CUDA_PagedAttention_sm100a"; }
+std::string PagedAttention::get_version() const { return ahpc_version(); }
+void PagedAttention::enable_profiling(bool enable) {
+    profiling_enabled_ = enable;
+    if (!enable) profiling_results_.clear();
+}
+std::vector<std::pair<std::string, double>> PagedAttention::get_profiling_results() const { return profiling_results_; }
+void PagedAttention::reset_profiling() { profiling_results_.clear(); }
+
+AttentionError PagedAttention::validate_inputs(const TensorShape& q, const TensorShape&, const TensorShape&, const TensorShape& o,
+                                               const AttentionParams& params) const {
+    for (const TensorShape* s : {&q, &o}) {
+        if (s->dimensions.size() != 4) return AttentionError::INVALID_INPUT;
+        if (s->dimensions[0] != params.batch_size || s->dimensions[2] != params.num_heads || s->dimensions[3] != params.head_dimension)
+            return AttentionError::INVALID_INPUT;
+    }
+    return AttentionError::SUCCESS;
+}
+
+// ---- sequences ---------------------------------------------------------------------------------
+
+const PagedAttention::Sequence* PagedAttention::find(size_t id) const {
+    auto it = sequences_.find(id);
+    return it == sequences_.end() ? nullptr : &it->second;
+}
+
+size_t PagedAttention::create_sequence(size_t max_length) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    if (!pool_) throw AttentionException(AttentionError::INVALID_PARAMETERS, "PagedAttention not configured. Call configure() first.");
+    int32_t slot = -1;
+    check(ahpc_pool_seq_create(pool_, &slot));
+    const size_t id = next_sequence_id_++;
+    sequences_[id] = Sequence{slot, max_length};
+    return id;
+}
+
+void PagedAttention::destroy_sequence(size_t sequence_id) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    auto it = sequences_.find(sequence_id);
+    if (it == sequences_.end()) return;                 // unknown ids are ignored (paged_attention.cpp:345-350)
+    check(ahpc_pool_seq_destroy(pool_, it->second.slot, stream_));
+    sequences_.erase(it);
+}
+
+void PagedAttention::reset_sequence(size_t sequence_id) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    if (const Sequence* s = find(sequence_id)) check(ahpc_pool_seq_truncate(pool_, s->slot, 0, stream_));
+}
+
+bool PagedAttention::is_sequence_active(size_t sequence_id) const {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    return find(sequence_id) != nullptr;
+}
+
+void PagedAttention::extend_sequence(size_t sequence_id, size_t additional_tokens) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    auto it = sequences_.find(sequence_id);
+    if (it != sequences_.end()) it->second.max_length += additional_tokens;   // pages are taken when tokens arrive
+}
+
+void PagedAttention::truncate_sequence(size_t sequence_id, size_t new_length) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    auto it = sequences_.find(sequence_id);
+    if (it == sequences_.end()) return;
+    check(ahpc_pool_seq_truncate(pool_, it->second.slot, static_cast<int32_t>(std::min<size_t>(new_length, 0x7fffffff)), stream_));
+    it->second.max_length = new_length;
+}
+
+size_t PagedAttention::get_sequence_length(size_t sequence_id) const {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    const Sequence* s = find(sequence_id);
+    return s ? static_cast<size_t>(std::max(0, ahpc_pool_seq_len(pool_, s->slot))) : 0;
+}
+
+size_t PagedAttention::get_max_sequence_length(size_t sequence_id) const {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    const Sequence* s = find(sequence_id);
+    return s ? s->max_length : 0;
+}
+
+size_t PagedAttention::used_bytes_locked() const {
+    if (!pool_) return 0;
+    const int64_t total = static_cast<int64_t>(
+        std::max(paged_config_.initial_page_pool_size,
+                 paged_config_.memory_pool_size / std::max<int64_t>(1, ahpc_pool_page_bytes(pool_))));
+    const int64_t used = std::max<int64_t>(0, total - ahpc_pool_free_pages(pool_));
+    return static_cast<size_t>(used * ahpc_pool_page_bytes(pool_));
+}
+
+void PagedAttention::note_usage_locked() { peak_memory_usage_ = std::max(peak_memory_usage_, used_bytes_locked()); }
+
+void PagedAttention::append_kv_cache(size_t sequence_id, const void* key_data, const void* value_data, size_t num_tokens, DataType data_type) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    const Sequence* s = find(sequence_id);
+    if (!s) throw AttentionException(AttentionError::INVALID_INPUT, "Sequence not found");
+    if (num_tokens == 0) return;
+    if (!key_data || !value_data) throw AttentionException(AttentionError::INVALID_INPUT, "Null tensor data pointer");
+    const int32_t slot = s->slot, n = static_cast<int32_t>(num_tokens);
+    check(ahpc_pool_append(pool_, &slot, &n, 1, key_data, value_data, static_cast<int32_t>(data_type), stream_));
+    note_usage_locked();
+}
+
+void PagedAttention::get_kv_cache(size_t sequence_id, void* key_data, void* value_data, size_t start_token, size_t num_tokens, DataType data_type) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    const Sequence* s = find(sequence_id);
+    if (!s) throw AttentionException(AttentionError::INVALID_INPUT, "Sequence not found");
+    check(ahpc_pool_gather(pool_, s->slot, static_cast<int32_t>(start_token), static_cast<int32_t>(num_tokens), key_data, value_data,
+                           static_cast<int32_t>(data_type), stream_));
+}
+
+void PagedAttention::clear_kv_cache(size_t sequence_id) { reset_sequence(sequence_id); }
+
+size_t PagedAttention::fork_sequence(size_t source_id, size_t n_prefix_tokens) {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    const Sequence* s = find(source_id);
+    if (!s) throw AttentionException(AttentionError::INVALID_INPUT, "Sequence not found");
+    int32_t slot = -1;
+    check(ahpc_pool_seq_fork(pool_, s->slot, static_cast<int32_t>(n_prefix_tokens), &slot, stream_));
+    const size_t id = next_sequence_id_++;
+    sequences_[id] = Sequence{slot, s->max_length};
+    note_usage_locked();
+    return id;
+}
+
+std::vector<int32_t> PagedAttention::get_block_table(size_t sequence_id) const {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    const Sequence* s = find(sequence_id);
+    if (!s) throw AttentionException(AttentionError::INVALID_INPUT, "Sequence not found");
+    const int32_t pages = std::max(0, ahpc_pool_seq_pages(pool_, s->slot));
+    std::vector<int32_t> out(pages);
+    if (pages) check(ahpc_pool_read_block_table(pool_, s->slot, out.data(), pages, stream_));
+    return out;
+}
+
+// ---- decode ------------------------------------------------------------------------------------
+
+void PagedAttention::forward_batch(const std::vector<size_t>& sequence_ids, const std::vector<TensorShape>& query_shapes,
+                                   const std::vector<const void*>& query_data, const std::vector<TensorShape>& output_shapes,
+                                   const std::vector<void*>& output_data, const std::vector<const void*>& attention_masks) {
+    if (!is_configured_)
+        throw AttentionException(AttentionError::INVALID_PARAMETERS, "PagedAttention not configured. Call configure() first.");
+    const auto t0 = std::chrono::steady_clock::now();
+    const size_t n = sequence_ids.size();
+    if (n != query_shapes.size() || n != query_data.size() || n != output_shapes.size() || n != output_data.size())
+        throw AttentionException(AttentionError::INVALID_INPUT, "Batch input sizes mismatch");
+    if (!attention_masks.empty())
+        for (const void* m : attention_masks)
+            if (m) throw AttentionException(AttentionError::UNSUPPORTED_OPERATION, "per-sequence masks are not supported in decode");
+    if (n == 0) return;
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    const size_t H = current_params_.num_heads, D = current_params_.head_dimension;
+    const DataType dt = query_shapes[0].data_type;
+    std::vector<int32_t> slots(n);
+    for (size_t i = 0; i < n; ++i) {
+        const Sequence* s = find(sequence_ids[i]);
+        if (!s) throw AttentionException(AttentionError::INVALID_INPUT, "Sequence not found");
+        slots[i] = s->slot;
+        if (!query_data[i] || !output_data[i]) throw AttentionException(AttentionError::INVALID_INPUT, "Null tensor data pointer");
+        if (query_shapes[i].total_elements() != H * D || output_shapes[i].total_elements() != H * D)
+            throw AttentionException(AttentionError::INVALID_INPUT, "decode expects one query token per sequence: shape {1,1,H,D}");
+        if (query_shapes[i].data_type != dt || output_shapes[i].data_type != dt)
+            throw AttentionException(AttentionError::INVALID_INPUT, "all queries and outputs of a batch must share one data type");
+    }
+    const size_t row_bytes = H * D * dtype_bytes(dt);
+    ahpc_decode_args a{};
+    a.pool = pool_;
+    a.qo_dtype = static_cast<int32_t>(dt);
+    a.scale = current_params_.scale_factor;
+    a.split_tokens = 0;
+    a.stream = stream_;
+
+    bool all_host = true, contiguous = true;
+    for (size_t i = 0; i < n; ++i) {
+        all_host = all_host && ahpc_pointer_is_host(query_data[i]) && ahpc_pointer_is_host(output_data[i]);
+        if (i) {
+            contiguous = contiguous && static_cast<const char*>(query_data[i]) == static_cast<const char*>(query_data[i - 1]) + row_bytes &&
+                         static_cast<char*>(output_data[i]) == static_cast<char*>(output_data[i - 1]) + row_bytes;
+        }
+    }
+    if (contiguous) {                                   // one launch straight on the caller's buffers
+        a.seqs = slots.data(); a.n_seqs = static_cast<int32_t>(n);
+        a.q = query_data[0]; a.out = output_data[0];
+        check(ahpc_paged_decode(&a));
+    } else if (all_host) {                              // separate host buffers: pack, one launch, unpack
+        std::vector<char> q(n * row_bytes), o(n * row_bytes);
+        for (size_t i = 0; i < n; ++i) std::memcpy(q.data() + i * row_bytes, query_data[i], row_bytes);
+        a.seqs = slots.data(); a.n_seqs = static_cast<int32_t>(n);
+        a.q = q.data(); a.out = o.data();
+        check(ahpc_paged_decode(&a));
+        for (size_t i = 0; i < n; ++i) std::memcpy(output_data[i], o.data() + i * row_bytes, row_bytes);
+    } else {                                            // scattered device buffers: one launch per sequence
+        for (size_t i = 0; i < n; ++i) {
+            a.seqs = &slots[i]; a.n_seqs = 1;
+            a.q = query_data[i]; a.out = output_data[i];
+            check(ahpc_paged_decode(&a));
+        }
+    }
+    if (profiling_enabled_) {
+        check(ahpc_stream_synchronize(device_, stream_));
+        profiling_results_.emplace_back("forward_batch", std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
+    }
+}
+
+// ---- statistics ----------------------------------------------------------------------------------
+
+size_t PagedAttention::get_total_memory_usage() const {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    return used_bytes_locked();
+}
+size_t PagedAttention::get_peak_memory_usage() const {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    return std::max(peak_memory_usage_, used_bytes_locked());
+}
+float PagedAttention::get_memory_utilization() const {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    return paged_config_.memory_pool_size ? static_cast<float>(used_bytes_locked()) / static_cast<float>(paged_config_.memory_pool_size) : 0.0f;
+}
+size_t PagedAttention::get_active_sequences_count() const {
+    std::lock_guard<std::mutex> lock(sequences_mutex_);
+    return sequences_.size();
+}
+
+void PagedAttention::compact_pages() {}                           // pages are fixed-size and position-free: nothing to defragment
+void PagedAttention::preload_pages(const std::vector<size_t>&) {} // the pool is resident in HBM
+
+}  // namespace attention_hpc

@@ -93,6 +93,13 @@ typedef struct ahpc_device_info {
 } ahpc_device_info;
 AHPC_API ahpc_status ahpc_get_device_info(int32_t device, ahpc_device_info* out);
 
+/* Blocks until the work enqueued on `stream` of `device` has finished.  Used by the C++ surface for
+ * its profiling entries (FlashAttention::forward times a completed pass, flash_attention.cpp:107-111). */
+AHPC_API ahpc_status ahpc_stream_synchronize(int32_t device, void* stream);
+
+/* 1 if `ptr` is ordinary host memory the library would stage, 0 if the GPU can address it directly. */
+AHPC_API int32_t ahpc_pointer_is_host(const void* ptr);
+
 /* ------------------------------------------------------------------------------------------
  * FlashAttention forward
  * Replaces launch_flash_attention_kernel (cuda_flash_attention.hpp:42-48), i.e. the body of

@@ -1,0 +1,131 @@
+// attention_hpc::PagedAttention on B200: the public surface the reference declares in
+// src/algorithms/paged_attention.hpp:176-263 (sequence management, KV-cache append / read-back,
+// forward_batch decode, memory statistics), backed by the device-resident page pool and the decode
+// kernels behind the C ABI of ahpc.h.  PagedAttentionConfig keeps the reference's fields (:125-149).
+#pragma once
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <utility>
+#include <vector>
+
+#include "api/attention_interface.hpp"
+
+struct ahpc_pool;
+
+#pragma GCC visibility push(default)
+namespace attention_hpc {
+
+struct PagedAttentionConfig {
+    size_t page_size = 16;
+    size_t max_pages_per_sequence = 1024;
+    size_t initial_page_pool_size = 64;
+    bool enable_page_caching = true;
+    bool enable_memory_prefetching = false;
+    size_t memory_pool_size = size_t(1024) * 1024 * 1024;   // bytes of KV the pool may hold
+    size_t max_concurrent_sequences = 32;
+    size_t block_size = 64;
+    bool enable_dynamic_batching = true;
+    bool use_kernel_fusion = false;
+    bool enable_async_copying = false;
+    size_t prefetch_distance = 2;
+    bool use_contiguous_layout = true;
+    bool enable_memory_coalescing = true;
+    // Addition: storage type of the pool (the reference stores float; FP16 halves the decode traffic).
+    DataType kv_cache_dtype = DataType::FLOAT16;
+};
+
+class PagedAttention : public AttentionInterface {
+public:
+    PagedAttention();
+    ~PagedAttention() override;
+    PagedAttention(const PagedAttention&) = delete;
+    PagedAttention& operator=(const PagedAttention&) = delete;
+
+    void configure(const AttentionParams& params, const PerformanceConfig& perf_config = PerformanceConfig{}) override;
+    void configure_paged_attention(const PagedAttentionConfig& paged_config);
+
+    // Dense attention of all query tokens over the given K/V (the reference's convenience path:
+    // temporary sequence, append, attend, destroy - src/algorithms/paged_attention.cpp:132-174).
+    void forward(const TensorShape& query_shape, const void* query_data, const TensorShape& key_shape, const void* key_data,
+                 const TensorShape& value_shape, const void* value_data, const TensorShape& output_shape, void* output_data,
+                 const void* attention_mask = nullptr) override;
+    void backward(const TensorShape& grad_output_shape, const void* grad_output_data, const TensorShape& query_shape, const void* query_data,
+                  const TensorShape& key_shape, const void* key_data, const TensorShape& value_shape, const void* value_data,
+                  const TensorShape& grad_query_shape, void* grad_query_data, const TensorShape& grad_key_shape, void* grad_key_data,
+                  const TensorShape& grad_value_shape, void* grad_value_data, const void* attention_mask = nullptr) override;
+
+    size_t get_workspace_size(const AttentionParams& params) const override;
+    void set_workspace(void* workspace_ptr, size_t workspace_size) override;
+    bool supports_data_type(DataType data_type) const override;
+    bool supports_memory_layout(MemoryLayout layout) const override;
+    std::string get_backend_name() const override;
+    std::string get_version() const override;
+    void enable_profiling(bool enable) override;
+    std::vector<std::pair<std::string, double>> get_profiling_results() const override;
+    void reset_profiling() override;
+    AttentionError validate_inputs(const TensorShape& query_shape, const TensorShape& key_shape, const TensorShape& value_shape,
+                                   const TensorShape& output_shape, const AttentionParams& params) const override;
+
+    // Sequences.  Ids start at 1 and are never reused (paged_attention.cpp:67, 336).
+    size_t create_sequence(size_t max_length);
+    void destroy_sequence(size_t sequence_id);
+    void reset_sequence(size_t sequence_id);
+    bool is_sequence_active(size_t sequence_id) const;
+    void extend_sequence(size_t sequence_id, size_t additional_tokens);
+    void truncate_sequence(size_t sequence_id, size_t new_length);
+    size_t get_sequence_length(size_t sequence_id) const;
+    size_t get_max_sequence_length(size_t sequence_id) const;
+
+    // K/V of `num_tokens` tokens as [num_tokens, num_heads, head_dimension] in `data_type` (host or device memory).
+    void append_kv_cache(size_t sequence_id, const void* key_data, const void* value_data, size_t num_tokens, DataType data_type);
+    void get_kv_cache(size_t sequence_id, void* key_data, void* value_data, size_t start_token, size_t num_tokens, DataType data_type);
+    void clear_kv_cache(size_t sequence_id);
+
+    // Decode: one query token per listed sequence, shapes {1,1,H,D}.
+    void forward_batch(const std::vector<size_t>& sequence_ids, const std::vector<TensorShape>& query_shapes,
+                       const std::vector<const void*>& query_data, const std::vector<TensorShape>& output_shapes,
+                       const std::vector<void*>& output_data, const std::vector<const void*>& attention_masks = {});
+
+    size_t get_total_memory_usage() const;
+    size_t get_peak_memory_usage() const;
+    float get_memory_utilization() const;
+    size_t get_active_sequences_count() const;
+
+    void compact_pages();
+    void preload_pages(const std::vector<size_t>& sequence_ids);
+
+    // Additions (no counterpart in the reference).
+    // New sequence sharing the first n_prefix_tokens of `source_id` (whole pages are shared by reference count).
+    size_t fork_sequence(size_t source_id, size_t n_prefix_tokens);
+    // The block-table row of a sequence, read back from the device.
+    std::vector<int32_t> get_block_table(size_t sequence_id) const;
+    void set_device(int device) { device_ = device; }
+    void set_stream(void* cuda_stream) { stream_ = cuda_stream; }
+
+private:
+    struct Sequence {
+        int32_t slot;
+        size_t max_length;
+    };
+    void create_pool();
+    void destroy_pool();
+    const Sequence* find(size_t id) const;
+    size_t used_bytes_locked() const;
+    void note_usage_locked();
+
+    PagedAttentionConfig paged_config_;
+    bool is_configured_ = false;
+    ahpc_pool* pool_ = nullptr;
+    std::unordered_map<size_t, Sequence> sequences_;
+    mutable std::mutex sequences_mutex_;
+    size_t next_sequence_id_ = 1;
+    size_t peak_memory_usage_ = 0;
+    std::vector<std::pair<std::string, double>> profiling_results_;
+    int device_ = 0;
+    void* stream_ = nullptr;
+};
+
+}  // namespace attention_hpc
+#pragma GCC visibility pop

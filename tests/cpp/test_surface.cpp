@@ -1,0 +1,305 @@
+// The reference's callers, restated against the C++ surface of this library with seeded inputs:
+// tests/test_flash_attention.cpp (fixture :99-138, cases :141-582), tests/test_backends.cpp
+// (:108-207, 631-680) and examples/basic_usage.cpp (:115-200).  Plain checks instead of gtest
+// (not installed); the CPU oracle (oracle/oracle.c) is the checker.  Needs a B200; exits non-zero on
+// the first failed check.
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "algorithms/flash_attention.hpp"
+#include "algorithms/paged_attention.hpp"
+#include "api/backend_factory.hpp"
+
+extern "C" {
+void oracle_attention_fwd(const float*, const float*, const float*, float*, float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                          const int64_t*, const int64_t*, const int64_t*, const int64_t*, float, int, const float*);
+void oracle_paged_decode(const float*, const float*, const float*, float*, const int32_t*, const int32_t*, int64_t, int64_t, int64_t,
+                         int64_t, int64_t, float);
+uint16_t oracle_f32_to_bf16(float);
+float oracle_bf16_to_f32(uint16_t);
+uint16_t oracle_f32_to_f16(float);
+float oracle_f16_to_f32(uint16_t);
+}
+
+using namespace attention_hpc;
+
+static int g_checks = 0;
+#define CHECK(cond)                                                                  \
+    do {                                                                             \
+        ++g_checks;                                                                  \
+        if (!(cond)) { std::printf("FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond); std::exit(1); } \
+    } while (0)
+#define CHECK_THROWS(stmt, code)                                                     \
+    do {                                                                             \
+        bool thrown = false;                                                         \
+        try { stmt; } catch (const AttentionException& e) { thrown = e.error_code() == (code); } \
+        ++g_checks;                                                                  \
+        if (!thrown) { std::printf("FAILED %s:%d: expected %s from %s\n", __FILE__, __LINE__, #code, #stmt); std::exit(1); } \
+    } while (0)
+
+static uint64_t g_state = 0x9E3779B97F4A7C15ull;
+static float uniform() {                         // uniform(-1, 1) like the reference's generate_random_data, but seeded
+    g_state = g_state * 6364136223846793005ull + 1442695040888963407ull;
+    return static_cast<float>((g_state >> 40) / double(1ull << 24)) * 2.0f - 1.0f;
+}
+static std::vector<float> random_data(size_t n) {
+    std::vector<float> v(n);
+    for (float& x : v) x = uniform();
+    return v;
+}
+
+static float max_abs_diff(const std::vector<float>& a, const std::vector<float>& b) {
+    float m = 0.f;
+    for (size_t i = 0; i < a.size(); ++i) m = std::fmax(m, std::fabs(a[i] - b[i]));
+    return m;
+}
+
+static std::vector<float> oracle(const std::vector<float>& q, const std::vector<float>& k, const std::vector<float>& v, size_t B, size_t H,
+                                 size_t S, size_t D, float scale, bool causal, const float* mask = nullptr) {
+    std::vector<float> out(q.size());
+    const int64_t st[4] = {int64_t(H * S * D), int64_t(S * D), int64_t(D), 1};     // [B,H,S,D]-contiguous, as the reference indexes
+    oracle_attention_fwd(q.data(), k.data(), v.data(), out.data(), nullptr, B, H, S, S, D, st, st, st, st, scale, causal, mask);
+    return out;
+}
+
+static void run_flash_case(FlashAttention& fa, AttentionParams params, float tol, const float* mask_data = nullptr) {
+    fa.configure(params);
+    const size_t n = params.batch_size * params.num_heads * params.sequence_length * params.head_dimension;
+    auto q = random_data(n), k = random_data(n), v = random_data(n);
+    std::vector<float> out(n, 0.0f);
+    TensorShape shape({params.batch_size, params.sequence_length, params.num_heads, params.head_dimension}, DataType::FLOAT32);
+    fa.forward(shape, q.data(), shape, k.data(), shape, v.data(), shape, out.data(), mask_data);
+    auto ref = oracle(q, k, v, params.batch_size, params.num_heads, params.sequence_length, params.head_dimension, params.scale_factor,
+                      params.causal_mask, mask_data);
+    CHECK(max_abs_diff(out, ref) <= tol);
+}
+
+static void test_factory() {
+    CHECK(BackendFactory::isBackendAvailable(BackendType::CUDA));
+    CHECK(!BackendFactory::isBackendAvailable(BackendType::CPU));          // no CPU fallback in the product
+    CHECK(!BackendFactory::isBackendAvailable(BackendType::OPENCL));
+    auto avail = BackendFactory::getAvailableBackends();
+    CHECK(avail.size() == 1 && avail[0] == BackendType::CUDA);
+    auto cap = BackendFactory::getBackendCapability(BackendType::CUDA);
+    CHECK(cap.available && cap.compute_capability_major == 10 && cap.supports_tensor_cores && cap.memory_size > 0);
+    for (BackendType t : {BackendType::CUDA, BackendType::AUTO}) {
+        auto b = BackendFactory::createFlashAttention(t);
+        CHECK(b != nullptr);
+        CHECK(b->get_backend_name().rfind(BackendFactory::backendTypeToString(BackendType::CUDA), 0) == 0);   // test_backends.cpp:194
+        CHECK(!b->get_version().empty());
+        CHECK(b->supports_data_type(DataType::BFLOAT16));
+    }
+    CHECK_THROWS(BackendFactory::createBackend(BackendType::CPU), AttentionError::BACKEND_NOT_AVAILABLE);
+    CHECK_THROWS(BackendFactory::createPagedAttention(BackendType::VULKAN), AttentionError::BACKEND_NOT_AVAILABLE);
+    CHECK(BackendFactory::selectBestBackend() == BackendType::CUDA);
+    CHECK(BackendFactory::selectBestBackend(std::vector<BackendType>{BackendType::OPENGL, BackendType::CUDA}) == BackendType::CUDA);
+    CHECK(BackendFactory::stringToBackendType("cuda") == BackendType::CUDA);
+    CHECK(BackendFactory::backendTypeToString(BackendType::VULKAN) == "Vulkan");
+    CHECK(!BackendFactory::getSystemInfo().empty());
+    // the plug-in hook: a creator that calls back into the factory must not deadlock
+    BackendFactory::registerBackend(BackendType::OPENCL, "Forwarder", [] { return BackendFactory::createFlashAttention(BackendType::CUDA); });
+    CHECK(BackendFactory::isBackendAvailable(BackendType::OPENCL));
+    CHECK(BackendFactory::createBackend(BackendType::OPENCL)->get_backend_name().rfind("CUDA", 0) == 0);
+    BackendFactory::unregisterBackend(BackendType::OPENCL);
+    CHECK(!BackendFactory::isBackendAvailable(BackendType::OPENCL));
+    // error handling of test_backends.cpp:631-680
+    auto b = BackendFactory::createFlashAttention(BackendType::CUDA);
+    TensorShape s({2, 16, 4, 64}, DataType::FLOAT32);
+    std::vector<float> buf(s.total_elements());
+    CHECK_THROWS(b->forward(s, buf.data(), s, buf.data(), s, buf.data(), s, buf.data()), AttentionError::INVALID_PARAMETERS);
+    AttentionParams zero{};
+    CHECK_THROWS(b->configure(zero), AttentionError::INVALID_PARAMETERS);
+}
+
+static void test_flash_attention() {
+    AttentionParams base{};
+    base.batch_size = 2; base.sequence_length = 16; base.num_heads = 4; base.head_dimension = 64;
+    base.causal_mask = false; base.scale_factor = 1.0f / std::sqrt(64.0f);
+    FlashAttention fa;
+    run_flash_case(fa, base, 1e-4f);                                  // ForwardPassSmallInput
+    AttentionParams causal = base; causal.causal_mask = true;
+    run_flash_case(fa, causal, 1e-4f);                                // CausalMaskTest
+    for (size_t s : {size_t(1), size_t(4), size_t(32), size_t(128)}) {   // DifferentSequenceLengths + EdgeCaseSequenceLength1
+        AttentionParams p = base; p.sequence_length = s;
+        run_flash_case(fa, p, 1e-4f);
+    }
+    for (size_t d : {size_t(16), size_t(32), size_t(64), size_t(128)}) { // DifferentHeadDimensions
+        AttentionParams p = base; p.head_dimension = d; p.scale_factor = 1.0f / std::sqrt(float(d));
+        run_flash_case(fa, p, std::fmax(1e-4f, 1e-5f * std::sqrt(float(d))));
+    }
+    {                                                                 // DifferentBlockSizes: block sizes are hints
+        FlashAttentionConfig c; c.block_size_q = 32; c.block_size_k = 32;
+        fa.configure(base); fa.configure_flash_attention(c);
+        run_flash_case(fa, base, 1e-4f);
+        fa.configure_flash_attention(FlashAttentionConfig{});
+    }
+    {                                                                 // AttentionMaskTest: first half of the keys visible
+        std::vector<float> mask(base.batch_size * base.sequence_length * base.sequence_length, 0.0f);
+        for (size_t b = 0; b < base.batch_size; ++b)
+            for (size_t q = 0; q < base.sequence_length; ++q)
+                for (size_t k = 0; k < base.sequence_length / 2; ++k) mask[(b * base.sequence_length + q) * base.sequence_length + k] = 1.0f;
+        run_flash_case(fa, base, 1e-4f, mask.data());
+    }
+    {                                                                 // InvalidInputs
+        fa.configure(base);
+        const size_t n = base.batch_size * base.num_heads * base.sequence_length * base.head_dimension;
+        auto q = random_data(n), k = random_data(n), v = random_data(n);
+        std::vector<float> out(n);
+        TensorShape ok({2, 16, 4, 64}, DataType::FLOAT32), wrong_dim({2, 16, 4, 74}, DataType::FLOAT32), wrong_batch({3, 16, 4, 64}, DataType::FLOAT32);
+        CHECK_THROWS(fa.forward(wrong_dim, q.data(), ok, k.data(), ok, v.data(), ok, out.data()), AttentionError::MEMORY_ALLOCATION_FAILED);
+        CHECK_THROWS(fa.forward(wrong_batch, q.data(), ok, k.data(), ok, v.data(), ok, out.data()), AttentionError::MEMORY_ALLOCATION_FAILED);
+        CHECK_THROWS(fa.forward(ok, nullptr, ok, k.data(), ok, v.data(), ok, out.data()), AttentionError::INVALID_INPUT);
+        CHECK_THROWS(fa.backward(ok, out.data(), ok, q.data(), ok, k.data(), ok, v.data(), ok, out.data(), ok, out.data(), ok, out.data()),
+                     AttentionError::UNSUPPORTED_OPERATION);
+        CHECK(fa.validate_inputs(ok, ok, ok, ok, base) == AttentionError::SUCCESS);
+        CHECK(fa.validate_inputs(wrong_dim, ok, ok, ok, base) == AttentionError::INVALID_INPUT);
+        bool threw = false;
+        try { fa.safe_forward(wrong_batch, q.data(), ok, k.data(), ok, v.data(), ok, out.data()); } catch (const AttentionException&) { threw = true; }
+        CHECK(threw);
+    }
+    {                                                                 // profiling entries (flash_attention.cpp:107-111)
+        fa.enable_profiling(true);
+        run_flash_case(fa, base, 1e-4f);
+        auto prof = fa.get_profiling_results();
+        CHECK(prof.size() == 1 && prof[0].first == "forward_pass" && prof[0].second > 0.0);
+        fa.reset_profiling();
+        CHECK(fa.get_profiling_results().empty());
+        fa.enable_profiling(false);
+    }
+    {                                                                 // BF16 goes to the tensor-core kernel
+        AttentionParams p = base; p.sequence_length = 300; p.head_dimension = 128; p.causal_mask = true; p.scale_factor = 0.0f;
+        fa.configure(p);
+        const size_t n = p.batch_size * p.num_heads * p.sequence_length * p.head_dimension;
+        std::vector<float> q(n), k(n), v(n), got(n);
+        std::vector<uint16_t> qb(n), kb(n), vb(n), ob(n);
+        for (size_t i = 0; i < n; ++i) {
+            qb[i] = oracle_f32_to_bf16(uniform()); kb[i] = oracle_f32_to_bf16(uniform()); vb[i] = oracle_f32_to_bf16(uniform());
+            q[i] = oracle_bf16_to_f32(qb[i]); k[i] = oracle_bf16_to_f32(kb[i]); v[i] = oracle_bf16_to_f32(vb[i]);
+        }
+        TensorShape s({p.batch_size, p.sequence_length, p.num_heads, p.head_dimension}, DataType::BFLOAT16);
+        fa.forward(s, qb.data(), s, kb.data(), s, vb.data(), s, ob.data());
+        CHECK(fa.last_kernel() == "tcgen05");
+        for (size_t i = 0; i < n; ++i) got[i] = oracle_bf16_to_f32(ob[i]);
+        auto ref = oracle(q, k, v, p.batch_size, p.num_heads, p.sequence_length, p.head_dimension, 1.0f / std::sqrt(128.0f), true);
+        CHECK(max_abs_diff(got, ref) <= 2e-2f);
+    }
+}
+
+static void test_paged_attention() {
+    AttentionParams params{};
+    params.batch_size = 1; params.sequence_length = 64; params.num_heads = 4; params.head_dimension = 64; params.page_size = 16;
+    auto backend = BackendFactory::createPagedAttention(BackendType::CUDA);
+    auto* paged = dynamic_cast<PagedAttention*>(backend.get());         // examples/basic_usage.cpp:145
+    CHECK(paged != nullptr);
+    CHECK(backend->get_backend_name().rfind("CUDA", 0) == 0);
+    CHECK_THROWS(paged->forward_batch({}, {}, {}, {}, {}), AttentionError::INVALID_PARAMETERS);   // before configure
+    PagedAttentionConfig cfg;
+    cfg.memory_pool_size = size_t(8) << 20;
+    cfg.max_concurrent_sequences = 8;
+    cfg.max_pages_per_sequence = 32;
+    paged->configure_paged_attention(cfg);
+    paged->configure(params);
+    const size_t H = 4, D = 64, PS = 16;
+
+    const size_t a = paged->create_sequence(256), b = paged->create_sequence(256);
+    CHECK(a == 1 && b == 2);                                            // ids start at 1 (paged_attention.cpp:67)
+    CHECK(paged->is_sequence_active(a) && !paged->is_sequence_active(99));
+    CHECK(paged->get_active_sequences_count() == 2 && paged->get_max_sequence_length(a) == 256);
+
+    const size_t lens[2] = {37, 100};
+    std::vector<std::vector<float>> K(2), V(2);
+    for (int i = 0; i < 2; ++i) {
+        K[i].resize(lens[i] * H * D); V[i].resize(lens[i] * H * D);
+        for (float& x : K[i]) x = oracle_f16_to_f32(oracle_f32_to_f16(uniform()));     // values exactly representable in the FP16 pool
+        for (float& x : V[i]) x = oracle_f16_to_f32(oracle_f32_to_f16(uniform()));
+    }
+    paged->append_kv_cache(a, K[0].data(), V[0].data(), 20, DataType::FLOAT32);         // two appends, crossing a page boundary
+    paged->append_kv_cache(b, K[1].data(), V[1].data(), lens[1], DataType::FLOAT32);
+    paged->append_kv_cache(a, K[0].data() + 20 * H * D, V[0].data() + 20 * H * D, 17, DataType::FLOAT32);
+    CHECK(paged->get_sequence_length(a) == 37 && paged->get_sequence_length(b) == 100 && paged->get_sequence_length(99) == 0);
+    CHECK(paged->get_total_memory_usage() > 0 && paged->get_peak_memory_usage() >= paged->get_total_memory_usage());
+    CHECK_THROWS(paged->append_kv_cache(99, K[0].data(), V[0].data(), 1, DataType::FLOAT32), AttentionError::INVALID_INPUT);
+
+    // FIFO allocation order: a got pages 0,1 (20 tokens), b 2..8 (100 tokens), then a's third page is 9
+    auto ta = paged->get_block_table(a), tb = paged->get_block_table(b);
+    CHECK(ta.size() == 3 && ta[0] == 0 && ta[1] == 1 && ta[2] == 9);
+    CHECK(tb.size() == 7 && tb[0] == 2 && tb[6] == 8);
+
+    // get_kv_cache round trip
+    std::vector<float> kb(10 * H * D), vb(10 * H * D);
+    paged->get_kv_cache(a, kb.data(), vb.data(), 12, 10, DataType::FLOAT32);
+    CHECK(std::memcmp(kb.data(), K[0].data() + 12 * H * D, kb.size() * 4) == 0);
+    CHECK(std::memcmp(vb.data(), V[0].data() + 12 * H * D, vb.size() * 4) == 0);
+
+    // decode through forward_batch with separate host buffers per sequence (basic_usage.cpp:170-198)
+    std::vector<std::vector<float>> q(2, std::vector<float>(H * D)), o(2, std::vector<float>(H * D));
+    for (auto& row : q) for (float& x : row) x = uniform();
+    TensorShape one({1, 1, H, D}, DataType::FLOAT32);
+    paged->enable_profiling(true);
+    paged->forward_batch({a, b}, {one, one}, {q[0].data(), q[1].data()}, {one, one}, {o[0].data(), o[1].data()});
+    CHECK(paged->get_profiling_results().size() == 1 && paged->get_profiling_results()[0].first == "forward_batch");
+    // oracle over canonical [page, slot, H, D] caches built from the block tables read back from the device
+    const size_t pages = 16;
+    std::vector<float> kc(pages * PS * H * D, 0.f), vc(kc.size(), 0.f), qq(2 * H * D), want(2 * H * D);
+    std::vector<int32_t> table(2 * 8, -1), sl = {37, 100};
+    for (int i = 0; i < 2; ++i) {
+        const auto& t = i == 0 ? ta : tb;
+        for (size_t p = 0; p < t.size(); ++p) table[i * 8 + p] = t[p];
+        for (size_t tok = 0; tok < lens[i]; ++tok) {
+            const size_t dst = (size_t(t[tok / PS]) * PS + tok % PS) * H * D;
+            std::memcpy(&kc[dst], &K[i][tok * H * D], H * D * 4);
+            std::memcpy(&vc[dst], &V[i][tok * H * D], H * D * 4);
+        }
+        std::memcpy(&qq[i * H * D], q[i].data(), H * D * 4);
+    }
+    oracle_paged_decode(qq.data(), kc.data(), vc.data(), want.data(), table.data(), sl.data(), 2, H, D, PS, 8, 1.0f / std::sqrt(float(D)));
+    for (int i = 0; i < 2; ++i)
+        for (size_t e = 0; e < H * D; ++e) CHECK(std::fabs(o[i][e] - want[i * H * D + e]) <= 1e-3f);
+
+    CHECK_THROWS(paged->forward_batch({a, b}, {one}, {q[0].data()}, {one}, {o[0].data()}), AttentionError::INVALID_INPUT);   // sizes mismatch
+    CHECK_THROWS(paged->forward_batch({size_t(99)}, {one}, {q[0].data()}, {one}, {o[0].data()}), AttentionError::INVALID_INPUT);
+
+    // prefix sharing, truncation, destruction
+    const size_t c = paged->fork_sequence(b, 64);
+    CHECK(c == 3 && paged->get_sequence_length(c) == 64);
+    auto tc = paged->get_block_table(c);
+    CHECK(tc.size() == 4 && tc[0] == tb[0] && tc[3] == tb[3]);
+    paged->truncate_sequence(a, 16);
+    CHECK(paged->get_sequence_length(a) == 16 && paged->get_block_table(a).size() == 1);
+    paged->clear_kv_cache(a);
+    CHECK(paged->get_sequence_length(a) == 0);
+    paged->destroy_sequence(b);
+    paged->destroy_sequence(99);                                        // unknown ids are ignored
+    CHECK(paged->get_active_sequences_count() == 2);
+    std::vector<float> oc(H * D);
+    paged->forward_batch({c}, {one}, {q[1].data()}, {one}, {oc.data()});   // the shared pages outlive b
+    std::vector<int32_t> t1(8, -1), l1 = {64};
+    for (size_t p = 0; p < tc.size(); ++p) t1[p] = tc[p];
+    std::vector<float> w1(H * D);
+    oracle_paged_decode(q[1].data(), kc.data(), vc.data(), w1.data(), t1.data(), l1.data(), 1, H, D, PS, 8, 1.0f / std::sqrt(float(D)));
+    for (size_t e = 0; e < H * D; ++e) CHECK(std::fabs(oc[e] - w1[e]) <= 1e-3f);
+
+    // the dense convenience path (PagedAttention::forward) equals plain attention
+    AttentionParams dense{}; dense.batch_size = 1; dense.sequence_length = 24; dense.num_heads = 4; dense.head_dimension = 64;
+    auto p2 = BackendFactory::createPagedAttention(BackendType::CUDA);
+    p2->configure(dense);
+    const size_t n = 24 * 4 * 64;
+    auto dq = random_data(n), dk = random_data(n), dv = random_data(n);
+    std::vector<float> dout(n);
+    TensorShape ds({1, 24, 4, 64}, DataType::FLOAT32);
+    p2->forward(ds, dq.data(), ds, dk.data(), ds, dv.data(), ds, dout.data());
+    CHECK(max_abs_diff(dout, oracle(dq, dk, dv, 1, 4, 24, 64, 0.125f, false)) <= 1e-4f);
+}
+
+int main() {
+    test_factory();
+    test_flash_attention();
+    test_paged_attention();
+    std::printf("test_surface: %d checks passed\n", g_checks);
+    return 0;
+}
