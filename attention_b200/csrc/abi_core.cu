@@ -158,7 +158,7 @@ ahpc_status ahpc_get_device_info(int32_t device, ahpc_device_info* out) {
 }
 
 ahpc_status ahpc_stream_synchronize(int32_t device, void* stream) {
-    AHPC_TRY(use_device(device));
+    ScopedDevice device_guard_(device); AHPC_TRY(device_guard_.status());
     AHPC_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     return AHPC_SUCCESS;
 }

@@ -39,6 +39,27 @@ ahpc_status fail(ahpc_status code, const char* fmt, ...) __attribute__((format(p
 ahpc_status use_device(int device);
 int sm_count(int device);
 
+// Makes `device` current for the lifetime of the object and puts the caller's device back afterwards,
+// so that a call into the library never changes the calling thread's current device.
+class ScopedDevice {
+public:
+    explicit ScopedDevice(int device) {
+        if (cudaGetDevice(&prev_) != cudaSuccess) { (void)cudaGetLastError(); prev_ = -1; }
+        status_ = use_device(device);
+        changed_ = status_ == AHPC_SUCCESS && prev_ >= 0 && prev_ != device;
+    }
+    ~ScopedDevice() {
+        if (changed_) (void)cudaSetDevice(prev_);
+    }
+    ScopedDevice(const ScopedDevice&) = delete;
+    ScopedDevice& operator=(const ScopedDevice&) = delete;
+    ahpc_status status() const { return status_; }
+private:
+    int prev_ = -1;
+    bool changed_ = false;
+    ahpc_status status_ = AHPC_SUCCESS;
+};
+
 // True when p points to memory the GPU cannot address directly (pageable or unknown host memory
 // is reported as "host"; pinned/managed/device memory as device-accessible).
 bool is_host_pointer(const void* p);

@@ -84,7 +84,7 @@ size_t ahpc_fa_workspace_bytes(int32_t dtype, int64_t batch, int64_t heads, int6
 
 ahpc_status ahpc_fa_read_error_word(int32_t device, int32_t* out) {
     if (!out) return fail(AHPC_INVALID_INPUT, "ahpc_fa_read_error_word: out is NULL");
-    AHPC_TRY(use_device(device));
+    ScopedDevice device_guard_(device); AHPC_TRY(device_guard_.status());
     int w = 0;
     AHPC_TRY(fa_tc_read_error_word(device, &w));
     *out = w;
@@ -93,7 +93,7 @@ ahpc_status ahpc_fa_read_error_word(int32_t device, int32_t* out) {
 
 ahpc_status ahpc_fa_fwd(const ahpc_fa_args* args) {
     AHPC_TRY(validate(args));
-    AHPC_TRY(use_device(args->device));
+    ScopedDevice device_guard_(args->device); AHPC_TRY(device_guard_.status());
     FaLaunch l;
     to_launch(args, l);
 

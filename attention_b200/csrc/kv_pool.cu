@@ -331,7 +331,7 @@ ahpc_status ahpc_pool_create(ahpc_pool** out, const ahpc_pool_config* c) {
             seen[v] = 1;
         }
     }
-    AHPC_TRY(use_device(c->device));
+    ScopedDevice device_guard_(c->device); AHPC_TRY(device_guard_.status());
     ahpc_pool* p = new ahpc_pool();
     p->cfg = *c;
     p->cfg.free_order = nullptr;
@@ -382,7 +382,8 @@ ahpc_status ahpc_pool_create(ahpc_pool** out, const ahpc_pool_config* c) {
 
 ahpc_status ahpc_pool_destroy(ahpc_pool* p) {
     if (!p) return AHPC_SUCCESS;
-    if (cudaSetDevice(p->cfg.device) == cudaSuccess) {
+    ScopedDevice device_guard_(p->cfg.device);
+    if (device_guard_.status() == AHPC_SUCCESS) {
         (void)cudaDeviceSynchronize();
         void* ptrs[] = {p->k_data, p->v_data, p->table, p->seq_len, p->seq_pages, p->refcount, p->ring, p->ctrl, p->call_args, p->scratch};
         for (void* q : ptrs) if (q) (void)cudaFree(q);
@@ -409,7 +410,7 @@ ahpc_status ahpc_pool_seq_destroy(ahpc_pool* p, int32_t seq, void* stream) {
     if (!p) return fail(AHPC_INVALID_INPUT, "ahpc_pool_seq_destroy: pool is NULL");
     std::lock_guard<std::mutex> lock(p->mu);
     AHPC_TRY(check_seq(p, seq, "ahpc_pool_seq_destroy"));
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     pool_release_kernel<<<1, ALLOC_THREADS, 0, (cudaStream_t)stream>>>(seq, 0, 0, 0, p->table, p->seq_len, p->seq_pages, p->refcount,
                                                                         p->ring, p->ctrl, p->cfg.num_pages, p->cfg.max_pages_per_seq);
     AHPC_CUDA_OK(cudaGetLastError());
@@ -424,7 +425,7 @@ ahpc_status ahpc_pool_seq_truncate(ahpc_pool* p, int32_t seq, int32_t new_len, v
     AHPC_TRY(check_seq(p, seq, "ahpc_pool_seq_truncate"));
     if (new_len < 0) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_seq_truncate: negative length");
     if (new_len >= p->h_len[seq]) return AHPC_SUCCESS;
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     const int keep = (new_len + p->cfg.page_size - 1) / p->cfg.page_size;
     pool_release_kernel<<<1, ALLOC_THREADS, 0, (cudaStream_t)stream>>>(seq, keep, new_len, 1, p->table, p->seq_len, p->seq_pages,
                                                                         p->refcount, p->ring, p->ctrl, p->cfg.num_pages,
@@ -444,7 +445,7 @@ ahpc_status ahpc_pool_seq_fork(ahpc_pool* p, int32_t src, int32_t n_prefix, int3
     AHPC_TRY(check_seq(p, src, "ahpc_pool_seq_fork"));
     if (n_prefix < 0 || n_prefix > p->h_len[src])
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_seq_fork: prefix %d exceeds the %d tokens of sequence %d", n_prefix, p->h_len[src], src);
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     cudaStream_t st = (cudaStream_t)stream;
     const int full = n_prefix / p->cfg.page_size, rem = n_prefix % p->cfg.page_size;
     if (rem && p->free_lower_bound < 1) {
@@ -487,7 +488,7 @@ ahpc_status ahpc_pool_append(ahpc_pool* p, const int32_t* seqs, const int32_t* n
     std::lock_guard<std::mutex> lock(p->mu);
     if (n > p->cfg.max_seqs) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_append: %d sequences listed, pool holds %d", n, p->cfg.max_seqs);
     cudaStream_t st = (cudaStream_t)stream;
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
 
     std::vector<int32_t> host_args(3 * (size_t)n);
     std::vector<uint8_t> listed(p->cfg.max_seqs, 0);
@@ -559,7 +560,7 @@ ahpc_status ahpc_pool_gather(ahpc_pool* p, int32_t seq, int32_t start, int32_t n
     if (start < 0 || n < 0 || (int64_t)start + n > p->h_len[seq])
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_gather: tokens [%d, %d) outside sequence of %d", start, start + n, p->h_len[seq]);
     if (n == 0) return AHPC_SUCCESS;
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     cudaStream_t st = (cudaStream_t)stream;
     const bool host_out = is_host_pointer(k_out) || is_host_pointer(v_out);
     const size_t bytes = (size_t)n * p->cfg.heads * p->cfg.head_dim * dtype_size(out_dtype);
@@ -597,7 +598,7 @@ ahpc_status ahpc_pool_read_block_table(ahpc_pool* p, int32_t seq, int32_t* out, 
     if (!p || !out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_block_table: NULL argument");
     if (seq < 0 || seq >= p->cfg.max_seqs) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_block_table: sequence %d out of range", seq);
     if (n < 0 || n > p->cfg.max_pages_per_seq) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_read_block_table: n out of range");
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     AHPC_CUDA_OK(cudaMemcpyAsync(out, p->table + (size_t)seq * p->cfg.max_pages_per_seq, n * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     AHPC_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
     return AHPC_SUCCESS;
@@ -606,7 +607,7 @@ ahpc_status ahpc_pool_read_block_table(ahpc_pool* p, int32_t seq, int32_t* out, 
 ahpc_status ahpc_pool_read_seq_lens(ahpc_pool* p, int32_t* out, int32_t n, void* stream) {
     if (!p || !out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_seq_lens: NULL argument");
     if (n < 0 || n > p->cfg.max_seqs) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_read_seq_lens: n out of range");
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     AHPC_CUDA_OK(cudaMemcpyAsync(out, p->seq_len, n * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     AHPC_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
     return AHPC_SUCCESS;
@@ -615,7 +616,7 @@ ahpc_status ahpc_pool_read_seq_lens(ahpc_pool* p, int32_t* out, int32_t n, void*
 ahpc_status ahpc_pool_read_refcounts(ahpc_pool* p, int32_t* out, int32_t n, void* stream) {
     if (!p || !out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_refcounts: NULL argument");
     if (n < 0 || n > p->cfg.num_pages) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_read_refcounts: n out of range");
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     AHPC_CUDA_OK(cudaMemcpyAsync(out, p->refcount, n * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     AHPC_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
     return AHPC_SUCCESS;
@@ -623,7 +624,7 @@ ahpc_status ahpc_pool_read_refcounts(ahpc_pool* p, int32_t* out, int32_t n, void
 
 ahpc_status ahpc_pool_read_free_ring(ahpc_pool* p, int32_t* out, int32_t n, int64_t* count_out, void* stream) {
     if (!p || !count_out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_free_ring: NULL argument");
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     cudaStream_t st = (cudaStream_t)stream;
     long long c[4];
     AHPC_CUDA_OK(cudaMemcpyAsync(c, p->ctrl, sizeof(c), cudaMemcpyDeviceToHost, st));
@@ -642,7 +643,7 @@ ahpc_status ahpc_pool_read_free_ring(ahpc_pool* p, int32_t* out, int32_t n, int6
 
 ahpc_status ahpc_pool_read_error_flag(ahpc_pool* p, int32_t* out, void* stream) {
     if (!p || !out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_read_error_flag: NULL argument");
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     long long c[4];
     AHPC_CUDA_OK(cudaMemcpyAsync(c, p->ctrl, sizeof(c), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     AHPC_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));

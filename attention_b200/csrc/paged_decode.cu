@@ -403,7 +403,7 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
     if (a->n_seqs > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode: at most 65535 sequences per call");
     if (p->cfg.heads > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode: at most 65535 heads");
     std::lock_guard<std::mutex> lock(p->mu);
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     cudaStream_t st = (cudaStream_t)a->stream;
     int max_len = 0;
     for (int i = 0; i < a->n_seqs; ++i) {
@@ -477,7 +477,7 @@ ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* a) {
     if (is_host_pointer(a->q) || is_host_pointer(a->out))
         return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode_static: q and out must be device pointers (staging host tensors would allocate)");
     std::lock_guard<std::mutex> lock(p->mu);
-    AHPC_TRY(use_device(p->cfg.device));
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     cudaStream_t st = (cudaStream_t)a->stream;
     int max_len = 0;
     for (int i = 0; i < a->n_seqs; ++i) {

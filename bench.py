@@ -290,7 +290,7 @@ def build_decode_pool(torch, cfg, rank: int):
     n = len(plan.ctx)
     pages_needed = int(sum((int(plan.ctx[i]) - int(plan.prefix_tokens[i]) + ps - 1) // ps for i in range(n))) + 16
     pool = ops.KVPool(num_pages=pages_needed, heads=cfg.heads, head_dim=cfg.head_dim, dtype=torch.float16, page_size=ps,
-                      max_seqs=n, max_pages_per_seq=(cfg.ctx_hi + ps - 1) // ps,
+                      max_seqs=n, max_pages_per_seq=(cfg.ctx_hi + ps - 1) // ps, device=torch.cuda.current_device(),
                       free_order=synth.page_permutation(pages_needed, cfg.seed + rank))
     g = torch.Generator(device="cuda").manual_seed(cfg.seed + 104729 * rank)
     seqs = [-1] * n

@@ -223,3 +223,24 @@ def test_unknown_sequence_is_rejected():
     assert e.value.status == 1
     with pytest.raises(abi.AhpcError):
         pool.append([0], [1], q, q)
+
+
+def test_library_calls_leave_the_current_device_alone_and_work_on_other_devices():
+    """A call into the library must not change the calling thread's current device; with a second GPU,
+    a pool and a forward on device 1 work while device 0 stays current."""
+    assert torch.cuda.current_device() == 0
+    dev = 1 if torch.cuda.device_count() > 1 else 0
+    pool = ops.KVPool(num_pages=8, heads=2, head_dim=64, max_seqs=2, max_pages_per_seq=4, device=dev)
+    s = pool.seq_create()
+    g = torch.Generator(device=f"cuda:{dev}").manual_seed(1)
+    k = torch.randn((20, 2, 64), generator=g, device=f"cuda:{dev}").half()
+    pool.append([s], [20], k, k)
+    q = torch.randn((1, 2, 64), generator=g, device=f"cuda:{dev}").half()
+    out = pool.decode([s], q)
+    want = torch.softmax((q[0].float().unsqueeze(1) @ k.float().permute(1, 2, 0)) / 8.0, dim=-1) @ k.float().permute(1, 0, 2)
+    assert float((out[0].float() - want.squeeze(1)).abs().max()) <= 2e-2
+    t = torch.randn((1, 2, 100, 64), generator=g, device=f"cuda:{dev}").bfloat16()
+    o2 = ops.flash_attention_forward(t, t, t, causal=True)
+    assert o2.device.index == dev and torch.isfinite(o2.float()).all()
+    assert torch.cuda.current_device() == 0
+    pool.close()
