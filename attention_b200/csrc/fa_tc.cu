@@ -109,6 +109,38 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// Two floats in one 64-bit register pair, and arithmetic on both halves at once (f32x2 instructions).
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack_u2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) {
     uint32_t r;
@@ -286,24 +318,23 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
             const int k0 = j * BN;
             const bool need_mask = (p.causal && k0 + BN - 1 > q0 + t * BM) || (k0 + BN > p.seq_kv);
-            float row_max = -INFINITY;
             if (need_mask) {
                 const int limit = p.causal ? min(p.seq_kv - 1, row) : p.seq_kv - 1;     // last visible key
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float x = __uint_as_float(sr[c][i]);
-                        if (k0 + c * 32 + i > limit) x = -INFINITY;
-                        sr[c][i] = __float_as_uint(x);
-                        row_max = fmaxf(row_max, x);
-                    }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) row_max = fmaxf(row_max, __uint_as_float(sr[c][i]));
+                    for (int i = 0; i < 32; ++i)
+                        if (k0 + c * 32 + i > limit) sr[c][i] = 0xff800000u;            // -inf
             }
+            // row maximum: four independent chains of 3-input max
+            float mx[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                mx[c] = max3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), -INFINITY);
+#pragma unroll
+                for (int i = 2; i < 32; i += 2) mx[c] = max3(mx[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+            }
+            const float row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
             if (j == 0) {
                 m_used = row_max;
@@ -315,32 +346,41 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     const float alpha = (m_used == -INFINITY) ? 0.f : exp2f((m_used - m_new) * p.scale_log2);
                     l_run *= alpha;
                     m_used = m_new;
+                    const uint64_t alpha2 = pack_f2(alpha, alpha);
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t orow[32];
-                        tmem_ld32(o_addr + c * 32, orow);
+                    for (int c = 0; c < D / 16; ++c) {
+                        uint32_t orow[16];
+                        tmem_ld16(o_addr + c * 16, orow);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-                        tmem_st32(o_addr + c * 32, orow);
+                        for (int i = 0; i < 16; i += 2) {
+                            const uint64_t v = mul2(pack_u2(orow[i], orow[i + 1]), alpha2);
+                            orow[i] = (uint32_t)v;
+                            orow[i + 1] = (uint32_t)(v >> 32);
+                        }
+                        tmem_st16(o_addr + c * 16, orow);
                     }
                 }
             }
             const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
             const float neg_m = -m_eff * p.scale_log2;
-            float psum = 0.f;
+            const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2), negm2 = pack_f2(neg_m, neg_m);
+            uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};                                // four packed partial row sums
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, neg_m));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, neg_m));
-                    psum += p0 + p1;
+                    const uint64_t x2 = fma2(pack_u2(sr[c][2 * i], sr[c][2 * i + 1]), scale2, negm2);
+                    const float p0 = fast_exp2(__uint_as_float((uint32_t)x2));
+                    const float p1 = fast_exp2(__uint_as_float((uint32_t)(x2 >> 32)));
+                    sum2[i & 3] = add2(sum2[i & 3], pack_f2(p0, p1));
                     packed[i] = pack2<BF16>(p0, p1);
                 }
                 tmem_st16(s_addr + c * 16, packed);
             }
+            const uint64_t tot = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
+            const float psum = __uint_as_float((uint32_t)tot) + __uint_as_float((uint32_t)(tot >> 32));
             l_run += psum;
             tmem_wait_st();
             tc_fence_before_sync();
