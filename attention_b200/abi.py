@@ -83,7 +83,8 @@ _lib = None
 
 
 def library_path() -> str:
-    return _build.LIB_PATH
+    """The library to load: AHPC_LIBRARY_PATH if set (for trying out another build), else the in-tree one."""
+    return os.environ.get("AHPC_LIBRARY_PATH") or _build.LIB_PATH
 
 
 def lib() -> C.CDLL:

@@ -301,8 +301,10 @@ def build_decode_pool(torch, cfg, rank: int):
         else:
             seqs[i] = pool.seq_create()
         fresh = int(plan.ctx[i]) - prefix
-        kv = torch.randn((2, fresh, cfg.heads, cfg.head_dim), generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
-        pool.append([seqs[i]], [fresh], kv[0], kv[1])
+        for at in range(0, fresh, 8192):                      # bounded temporaries
+            m = min(8192, fresh - at)
+            kv = torch.randn((2, m, cfg.heads, cfg.head_dim), generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
+            pool.append([seqs[i]], [m], kv[0], kv[1])
     q = torch.randn((n, cfg.heads, cfg.head_dim), generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
     return pool, seqs, q, plan
 
@@ -381,6 +383,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["fa_c2", "fa_c4"], default="fa_c2")
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode section")
+    ap.add_argument("--decode", choices=["c3", "c5"], default="c3",
+                    help="paged-decode configuration: c3 (batch 64, U[512,8192]) or c5 (batch 256, logU[1024,32768], shared prefixes)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-small", action="store_true",
                     help="reduced copies of the workloads for profiler captures: FA B=2 H=16 S=4096 D=128 causal BF16, "
@@ -390,7 +394,7 @@ def main():
 
     from attention_b200 import synth
     cfg = synth.C2 if args.workload == "fa_c2" else synth.C4
-    dec_cfg = synth.C3
+    dec_cfg = synth.C3 if args.decode == "c3" else synth.C5
     if args.profile_small:
         import dataclasses
         cfg = dataclasses.replace(synth.C2, name="C2-small", batch=2, heads=16)
