@@ -43,9 +43,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (None until a capture exists for that kernel).
-# FA: 165 MB per launch on a quarter of C2 (profiles/fa_fwd_tc_kernel_c2small.md), scaled by the units processed.
+# FA: 159 MB per launch on a quarter of C2 (profiles/fa_fwd_tc_kernel_c2small.md), scaled by the units processed.
 # Decode: read+write = 1.0057 x the algorithmic bytes (profiles/paged_decode_kernel_c3small.md).
-NCU_TRAFFIC = {"fa_fwd_tc_kernel_bytes_per_bh_pair_s4096": 165.3e6 / 32, "paged_decode_kernel_ratio": 1.0057}
+NCU_TRAFFIC = {"fa_fwd_tc_kernel_bytes_per_bh_pair_s4096": 158.9e6 / 32, "paged_decode_kernel_ratio": 1.0057}
 
 
 def load_peaks():
