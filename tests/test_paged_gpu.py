@@ -244,3 +244,25 @@ def test_library_calls_leave_the_current_device_alone_and_work_on_other_devices(
     assert o2.device.index == dev and torch.isfinite(o2.float()).all()
     assert torch.cuda.current_device() == 0
     pool.close()
+
+
+def test_free_page_lower_bound_is_refreshed_from_the_device_when_needed():
+    """The host only keeps a lower bound of the free pages while pages are shared; an append that the
+    bound alone would refuse must succeed after the exact count is read back."""
+    m = Mirror(num_pages=10, heads=1, head_dim=64, max_seqs=4, max_pages=10, seed=9, permute=False)
+    a = m.create()
+    m.append([a], [64])
+    b = m.pool.seq_fork(a, 64)
+    assert b == m.model.fork(a, 64)[0]
+    m.pool.seq_destroy(a)
+    m.model.seq_destroy(a)
+    m.append([b], [16])
+    m.pool.seq_destroy(b)
+    m.model.seq_destroy(b)
+    assert m.model.free_count() == 10
+    assert m.pool.free_pages_lower_bound() < 10          # shared pages were not counted as freed
+    c = m.create()
+    m.append([c], [16 * 8])                              # needs 8 pages: more than the bound, fewer than the truth
+    m.check_tables()
+    assert m.pool.free_pages_lower_bound() == 2
+    m.decode_check([c])
