@@ -386,6 +386,9 @@ def main():
     ap.add_argument("--decode", choices=["c3", "c5"], default="c3",
                     help="paged-decode configuration: c3 (batch 64, U[512,8192]) or c5 (batch 256, logU[1024,32768], shared prefixes)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--strong", action="store_true",
+                    help="strong scaling: the heads of ONE configuration are split over the ranks (ahpc_shard_range) instead of "
+                         "every rank running a full copy; heads must divide by the number of ranks")
     ap.add_argument("--profile-small", action="store_true",
                     help="reduced copies of the workloads for profiler captures: FA B=2 H=16 S=4096 D=128 causal BF16, "
                          "decode = the first 16 sequences of C3; no end-to-end or CPU legs")
@@ -395,6 +398,17 @@ def main():
     from attention_b200 import synth
     cfg = synth.C2 if args.workload == "fa_c2" else synth.C4
     dec_cfg = synth.C3 if args.decode == "c3" else synth.C5
+    scaling = "weak"
+    if args.strong and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import dataclasses
+        from attention_b200 import abi
+        w, r = int(os.environ["WORLD_SIZE"]), int(os.environ.get("RANK", "0"))
+        hb, he = abi.shard_range(cfg.heads, w, r)
+        db, de = abi.shard_range(dec_cfg.heads, w, r)
+        assert cfg.heads % w == 0 and dec_cfg.heads % w == 0, "--strong needs heads divisible by the number of ranks"
+        cfg = dataclasses.replace(cfg, heads=he - hb)
+        dec_cfg = dataclasses.replace(dec_cfg, heads=de - db)
+        scaling = "strong"
     if args.profile_small:
         import dataclasses
         cfg = dataclasses.replace(synth.C2, name="C2-small", batch=2, heads=16)
@@ -427,9 +441,10 @@ def main():
     if rank == 0:
         line = {
             "metric": "flashattn_fwd_tflops", "value": fa["value"], "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": fa["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": fa["ms_per_step"], "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
-            "config": {"workload": workload_name(cfg), "per_gpu_batch": cfg.batch, "global_batch": cfg.batch * world,
+            "config": {"workload": workload_name(cfg), "per_gpu_batch": cfg.batch, "global_batch": cfg.batch * (1 if scaling == "strong" else world),
+                       "per_gpu_heads": cfg.heads,
                        "partition": "(batch, head) ranges per GPU, no collective",
                        "l2": f"inputs + output of a step ({4 * cfg.batch * cfg.heads * cfg.seq * cfg.head_dim * 2 / 1e6:.0f} MB) "
                              "exceed the 126 MB L2; no explicit flush"},
