@@ -13,7 +13,7 @@ from . import build as _build
 
 F32, F16, BF16 = 0, 1, 2
 LAYOUT_BHSD, LAYOUT_BSHD = 0, 1
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC = 0, 1, 2
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC, KERNEL_TC_TWO_TILE, KERNEL_TC_DOUBLE_S = 0, 1, 2, 3, 4
 
 STATUS_NAMES = {
     0: "SUCCESS", 1: "INVALID_INPUT", 2: "INVALID_PARAMETERS", 3: "MEMORY_ALLOCATION_FAILED",

@@ -26,7 +26,7 @@ ahpc_status validate(const ahpc_fa_args* a) {
     for (int t = 0; t < 4; ++t)
         for (int i = 0; i < 4; ++i)
             if (sts[t][i] < 0) return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: negative stride");
-    if (a->kernel < AHPC_FA_KERNEL_AUTO || a->kernel > AHPC_FA_KERNEL_TC)
+    if (a->kernel < AHPC_FA_KERNEL_AUTO || a->kernel > AHPC_FA_KERNEL_TC_DOUBLE_S)
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: unknown kernel selector %d", a->kernel);
     if (!std::isfinite(a->scale)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: scale is not finite");
     return AHPC_SUCCESS;
@@ -50,7 +50,7 @@ int pick_kernel(const FaLaunch& l, int requested, const char** why) {
     bool tc_ok = fa_tc_supported(l, &reason);
     if (why) *why = reason;
     if (requested == AHPC_FA_KERNEL_SIMT) return AHPC_FA_KERNEL_SIMT;
-    if (requested == AHPC_FA_KERNEL_TC) return tc_ok ? AHPC_FA_KERNEL_TC : -1;
+    if (requested >= AHPC_FA_KERNEL_TC) return tc_ok ? requested : -1;      // _TC leaves the choice of variant to the launcher
     return tc_ok ? AHPC_FA_KERNEL_TC : AHPC_FA_KERNEL_SIMT;
 }
 
@@ -58,7 +58,7 @@ ahpc_status run(const FaLaunch& l, int requested) {
     const char* why = nullptr;
     int kernel = pick_kernel(l, requested, &why);
     if (kernel < 0) return fail(AHPC_UNSUPPORTED_OPERATION, "tensor-core kernel not applicable: %s", why ? why : "?");
-    return kernel == AHPC_FA_KERNEL_TC ? launch_fa_tc(l) : launch_fa_simt(l);
+    return kernel == AHPC_FA_KERNEL_SIMT ? launch_fa_simt(l) : launch_fa_tc(l, kernel);
 }
 
 }  // namespace

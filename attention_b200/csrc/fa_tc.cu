@@ -25,27 +25,16 @@
 // Every wait in this kernel is bounded: when a barrier does not complete within the limit the
 // waiting thread records a code in a global error word, raises a CTA-wide abort flag, and every
 // role leaves its loop; tensor memory is then released and the kernel returns.
-#include <cuda.h>
-
-#include <cmath>
 #include <map>
 #include <mutex>
 
-#include "common.cuh"
-#include "sm100_ptx.cuh"
+#include "fa_tc_common.cuh"
 
 namespace ahpc {
 namespace {
 
 using namespace ptx;
-
-constexpr int BM = 128;                    // query rows per tile
-constexpr int BN = 128;                    // keys per tile
-constexpr int TC_THREADS = 320;
-constexpr int MMA_WARP = 8, TMA_WARP = 9;
-constexpr uint32_t TMEM_COLS = 512;
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about two seconds
-constexpr float RESCALE_THRESHOLD = 8.0f;               // in base-2 exponent units
+using namespace tc;
 
 template <int D> struct Cfg {
     static constexpr int SUBTILES = D / 64;                 // 64-element (128-byte) wide column blocks
@@ -66,6 +55,8 @@ struct TcParams {
     int causal;
     int n_pairs;
     int* error_word;
+    const int* redo;     // when set: per 128-row tile flags [tile][batch*heads]; only flagged pairs are computed
+    int n_tiles;
 };
 
 struct Barriers {        // one uint64 each, in shared memory
@@ -73,85 +64,6 @@ struct Barriers {        // one uint64 each, in shared memory
     uint32_t tmem_base;
     int abort;
 };
-
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word, int code) {
-    long long t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 127u) == 127u) {
-            if (*abort_flag) return false;
-            const long long now = clock64();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicCAS(error_word, 0, code);
-                return false;
-            }
-        }
-    }
-}
-
-// Key tiles the 128-row query tile starting at row r0 needs.
-__device__ __forceinline__ int kv_tiles_for(int r0, int seq_q, int seq_kv, int causal) {
-    if (r0 >= seq_q) return 0;
-    int n = (seq_kv + BN - 1) / BN;
-    if (causal) {
-        const int last_row = min(r0 + BM, seq_q) - 1;
-        n = min(n, last_row / BN + 1);
-    }
-    return n;
-}
-
-// 2^x on the special-function unit; -inf gives +0.
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float r;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-// Two floats in one 64-bit register pair, and arithmetic on both halves at once (f32x2 instructions).
-__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ uint64_t pack_u2(uint32_t lo, uint32_t hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-    return r;
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-
-template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
-template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-template <> __device__ __forceinline__ uint32_t pack2<false>(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -168,15 +80,24 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // which (pair of query tiles, batch, head): heavy (late) pairs first when causal
+    // Which (pair of query tiles, batch, head).  Consecutive CTAs are the pairs of ONE (batch, head), so the CTAs
+    // resident at any time share a few K/V streams and those stay in L2; heavy (late) pairs first when causal.
     const int bh_count = p.batch * p.heads;
-    const int pair_slot = blockIdx.x / bh_count, bh = blockIdx.x % bh_count;
+    const int bh = blockIdx.x / p.n_pairs, pair_slot = blockIdx.x % p.n_pairs;
     const int pair = p.causal ? p.n_pairs - 1 - pair_slot : pair_slot;
     const int b = bh / p.heads, h = bh % p.heads;
     const int q0 = pair * 2 * BM;
     const int n_t0 = kv_tiles_for(q0, p.seq_q, p.seq_kv, p.causal);
     const int n_t1 = kv_tiles_for(q0 + BM, p.seq_q, p.seq_kv, p.causal);
     const int n_kv = max(n_t0, n_t1);
+
+    if (p.redo) {
+        // second pass behind fa_fwd_tc2_kernel: only the tiles that kernel flagged are recomputed
+        const int t0 = 2 * pair;
+        const bool wanted = p.redo[(long long)t0 * bh_count + bh] != 0 ||
+                            (t0 + 1 < p.n_tiles && p.redo[(long long)(t0 + 1) * bh_count + bh] != 0);
+        if (!wanted) return;
+    }
 
     if (threadIdx.x == MMA_WARP * 32) {
         for (int t = 0; t < 2; ++t) {
@@ -423,8 +344,24 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 }
 
+template <int D, bool BF16>
+ahpc_status launch(const FaLaunch& a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcParams& p) {
+    using C = Cfg<D>;
+    auto kernel = fa_fwd_tc_kernel<D, BF16>;
+    AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
+    const long long ctas = (long long)p.n_pairs * a.batch * a.heads;
+    kernel<<<(unsigned)ctas, TC_THREADS, C::SMEM_BYTES, a.stream>>>(mq, mk, mv, p);
+    AHPC_CUDA_OK(cudaGetLastError());
+    return AHPC_SUCCESS;
+}
+
+}  // namespace
+
+namespace tc {
+
 // ---- host side --------------------------------------------------------------------------------
 
+namespace {
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -441,13 +378,14 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 4-d view (dim, position, head, batch) of a [B,H,S,D] tensor with element strides st; box 64 x 128.
-ahpc_status make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D, const int64_t st[4]) {
+}  // namespace
+
+ahpc_status make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D, const int64_t st[4], int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(AHPC_BACKEND_NOT_AVAILABLE, "cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
     const cuuint64_t strides[3] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[0] * 2};
-    const cuuint32_t box[4] = {64, BN, 1, 1};
+    const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
     const cuuint32_t elem[4] = {1, 1, 1, 1};
     CUresult r = fn(map, dtype == AHPC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                     const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -456,6 +394,7 @@ ahpc_status make_map(CUtensorMap* map, const void* base, int dtype, int B, int H
     return AHPC_SUCCESS;
 }
 
+namespace {
 struct ErrorWords {
     std::mutex mu;
     std::map<int, int*> per_device;
@@ -464,6 +403,8 @@ ErrorWords& error_words() {
     static ErrorWords e;
     return e;
 }
+}  // namespace
+
 ahpc_status error_word_for(int device, int** out) {
     ErrorWords& e = error_words();
     std::lock_guard<std::mutex> lock(e.mu);
@@ -486,18 +427,9 @@ bool map_ok(const void* ptr, const int64_t st[4]) {
     return true;
 }
 
-template <int D, bool BF16>
-ahpc_status launch(const FaLaunch& a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcParams& p) {
-    using C = Cfg<D>;
-    auto kernel = fa_fwd_tc_kernel<D, BF16>;
-    AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
-    const long long ctas = (long long)p.n_pairs * a.batch * a.heads;
-    kernel<<<(unsigned)ctas, TC_THREADS, C::SMEM_BYTES, a.stream>>>(mq, mk, mv, p);
-    AHPC_CUDA_OK(cudaGetLastError());
-    return AHPC_SUCCESS;
-}
+}  // namespace tc
 
-}  // namespace
+using namespace tc;
 
 bool fa_tc_supported(const FaLaunch& a, const char** why) {
     const char* r = nullptr;
@@ -513,9 +445,36 @@ bool fa_tc_supported(const FaLaunch& a, const char** why) {
     return r == nullptr;
 }
 
-ahpc_status launch_fa_tc(const FaLaunch& a) {
-    const char* why = nullptr;
-    if (!fa_tc_supported(a, &why)) return fail(AHPC_UNSUPPORTED_OPERATION, "tensor-core kernel not applicable: %s", why);
+namespace {
+
+// Flags written by fa_fwd_tc2_kernel and read by the second pass.  Each launch takes the next range of
+// a per-device ring, so launches in flight on different streams do not share flags until the ring
+// (1 Mi entries) has wrapped completely.
+constexpr long long REDO_RING_ENTRIES = 1ll << 20;
+struct RedoRing {
+    std::mutex mu;
+    std::map<int, std::pair<int*, long long>> per_device;   // base, cursor
+};
+RedoRing& redo_ring() {
+    static RedoRing r;
+    return r;
+}
+ahpc_status redo_flags_for(int device, long long n, int** out) {
+    RedoRing& r = redo_ring();
+    std::lock_guard<std::mutex> lock(r.mu);
+    auto it = r.per_device.find(device);
+    if (it == r.per_device.end()) {
+        int* base = nullptr;
+        AHPC_CUDA_OK(cudaMalloc(&base, REDO_RING_ENTRIES * sizeof(int)));
+        it = r.per_device.emplace(device, std::make_pair(base, 0ll)).first;
+    }
+    if (it->second.second + n > REDO_RING_ENTRIES) it->second.second = 0;
+    *out = it->second.first + it->second.second;
+    it->second.second += n;
+    return AHPC_SUCCESS;
+}
+
+ahpc_status launch_two_tile(const FaLaunch& a, const int* redo) {
     CUtensorMap mq, mk, mv;
     AHPC_TRY(make_map(&mq, a.q, a.dtype, a.batch, a.heads, a.seq_q, a.head_dim, a.qs));
     AHPC_TRY(make_map(&mk, a.k, a.dtype, a.batch, a.heads, a.seq_kv, a.head_dim, a.ks));
@@ -528,10 +487,27 @@ ahpc_status launch_fa_tc(const FaLaunch& a) {
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.causal = a.causal;
     p.n_pairs = (a.seq_q + 2 * BM - 1) / (2 * BM);
+    p.n_tiles = (a.seq_q + BM - 1) / BM;
+    p.redo = redo;
     AHPC_TRY(error_word_for(a.device, &p.error_word));
     const bool bf16 = a.dtype == AHPC_BF16;
     if (a.head_dim == 128) return bf16 ? launch<128, true>(a, mq, mk, mv, p) : launch<128, false>(a, mq, mk, mv, p);
     return bf16 ? launch<64, true>(a, mq, mk, mv, p) : launch<64, false>(a, mq, mk, mv, p);
+}
+
+}  // namespace
+
+ahpc_status launch_fa_tc(const FaLaunch& a, int variant) {
+    const char* why = nullptr;
+    if (!fa_tc_supported(a, &why)) return fail(AHPC_UNSUPPORTED_OPERATION, "tensor-core kernel not applicable: %s", why);
+    const long long tiles = (long long)((a.seq_q + BM - 1) / BM) * a.batch * a.heads;
+    if (variant != AHPC_FA_KERNEL_TC_DOUBLE_S || tiles > REDO_RING_ENTRIES || tiles > 2147483647ll)
+        return launch_two_tile(a, nullptr);
+    // double-buffered-score kernel, then the two-tile kernel over the tiles it flagged (normally none)
+    int* redo = nullptr;
+    AHPC_TRY(redo_flags_for(a.device, tiles, &redo));
+    AHPC_TRY(launch_fa_tc2(a, redo));
+    return launch_two_tile(a, redo);
 }
 
 // Non-zero when a kernel of this file gave up on a wait since the last call (synchronises the device).

@@ -1,0 +1,117 @@
+// Pieces shared by the tensor-core FlashAttention kernels (fa_tc.cu, fa_tc2.cu): tile constants,
+// the bounded mbarrier wait, packed-float arithmetic helpers and the host-side tensor-map and
+// scratch helpers.
+#pragma once
+
+#include <cuda.h>
+
+#include <cmath>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ahpc {
+namespace tc {
+
+using namespace ptx;
+
+constexpr int BM = 128;                    // query rows per tile
+constexpr int BN = 128;                    // keys per tile
+constexpr int TC_THREADS = 320;
+constexpr int MMA_WARP = 8, TMA_WARP = 9;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about two seconds
+constexpr float RESCALE_THRESHOLD = 8.0f;               // in base-2 exponent units
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word, int code) {
+    long long t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 127u) == 127u) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(error_word, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// Key tiles the 128-row query tile starting at row r0 needs.
+__device__ __forceinline__ int kv_tiles_for(int r0, int seq_q, int seq_kv, int causal) {
+    if (r0 >= seq_q) return 0;
+    int n = (seq_kv + BN - 1) / BN;
+    if (causal) {
+        const int last_row = min(r0 + BM, seq_q) - 1;
+        n = min(n, last_row / BN + 1);
+    }
+    return n;
+}
+
+// 2^x on the special-function unit; -inf gives +0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// Two floats in one 64-bit register pair, and arithmetic on both halves at once (f32x2 instructions).
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack_u2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+template <> __device__ __forceinline__ uint32_t pack2<false>(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+
+// ---- host helpers (defined in fa_tc.cu) ----------------------------------------------------------
+// 4-d tensor map (dim, position, head, batch) over a [B,H,S,D] view with element strides st; the box
+// is 64 elements (128 bytes, swizzled) by `box_rows` positions.
+ahpc_status make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D, const int64_t st[4],
+                     int box_rows = BN);
+// Per-device word in which a kernel records the code of a wait that gave up.
+ahpc_status error_word_for(int device, int** out);
+// True when a [B,H,S,D] view with these strides can be described by a tensor map.
+bool map_ok(const void* ptr, const int64_t st[4]);
+
+}  // namespace tc
+}  // namespace ahpc

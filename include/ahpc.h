@@ -64,7 +64,11 @@ enum { AHPC_LAYOUT_BHSD = 0, AHPC_LAYOUT_BSHD = 1 };
 enum {
     AHPC_FA_KERNEL_AUTO = 0,   /* tensor-core kernel when the shape allows, else SIMT */
     AHPC_FA_KERNEL_SIMT = 1,   /* FP32-FMA kernel (all dtypes, masks, any head_dim % 4 == 0 up to 256) */
-    AHPC_FA_KERNEL_TC = 2      /* tcgen05/TMEM kernel (FP16/BF16, head_dim 64 or 128, no explicit mask) */
+    AHPC_FA_KERNEL_TC = 2,     /* tcgen05/TMEM kernel (FP16/BF16, head_dim 64 or 128, no explicit mask): the library's
+                                  choice among the tensor-core kernels below */
+    AHPC_FA_KERNEL_TC_TWO_TILE = 3,  /* two 128-row query tiles per CTA, rescaling online softmax */
+    AHPC_FA_KERNEL_TC_DOUBLE_S = 4   /* one query tile per CTA, score tile double-buffered, fixed reference maximum;
+                                        followed by the two-tile kernel over the tiles it flagged (normally none) */
 };
 
 /* ------------------------------------------------------------------------------------------
@@ -145,7 +149,7 @@ AHPC_API size_t ahpc_fa_workspace_bytes(int32_t dtype, int64_t batch, int64_t he
  * reference, whose kernels have no waits.) */
 AHPC_API ahpc_status ahpc_fa_read_error_word(int32_t device, int32_t* out);
 
-/* Which kernel ahpc_fa_fwd would run for these arguments (AHPC_FA_KERNEL_SIMT or _TC);
+/* Which kernel ahpc_fa_fwd would run for these arguments (AHPC_FA_KERNEL_SIMT, or _TC / the _TC_* variant asked for);
  * a negative value means the arguments are invalid. */
 AHPC_API int32_t ahpc_fa_select_kernel(const ahpc_fa_args* args);
 

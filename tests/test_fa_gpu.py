@@ -126,18 +126,23 @@ def _error_word():
     return w.value
 
 
+TC_VARIANTS = [abi.KERNEL_TC_TWO_TILE, abi.KERNEL_TC_DOUBLE_S]
+
+
 @pytest.mark.parametrize("S", [1, 17, 128, 129, 255, 256, 257, 640, 1000])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("dtype,D", [("bf16", 128), ("f16", 64)])
-def test_tc_sequence_lengths(S, causal, dtype, D):
-    run_case(2, 3, S, S, D, dtype, causal, 500 + S, kernel=abi.KERNEL_TC)
+@pytest.mark.parametrize("kernel", TC_VARIANTS)
+def test_tc_sequence_lengths(S, causal, dtype, D, kernel):
+    run_case(2, 3, S, S, D, dtype, causal, 500 + S, kernel=kernel)
     assert _error_word() == 0
 
 
 @pytest.mark.parametrize("dtype,D", [("f16", 128), ("bf16", 64)])
-def test_tc_rectangular(dtype, D):
-    run_case(1, 2, 300, 700, D, dtype, False, 31, kernel=abi.KERNEL_TC)
-    run_case(1, 2, 700, 300, D, dtype, True, 32, kernel=abi.KERNEL_TC)
+@pytest.mark.parametrize("kernel", TC_VARIANTS)
+def test_tc_rectangular(dtype, D, kernel):
+    run_case(1, 2, 300, 700, D, dtype, False, 31, kernel=kernel)
+    run_case(1, 2, 700, 300, D, dtype, True, 32, kernel=kernel)
     assert _error_word() == 0
 
 
@@ -151,18 +156,24 @@ def test_tc_is_the_default_for_16bit_and_bshd_views_work():
     assert _error_word() == 0
 
 
-def test_tc_large_scores_exercise_the_lazy_rescale():
-    """Inputs scaled so that row maxima keep growing along the keys: the accumulator rescale path runs."""
+@pytest.mark.parametrize("kernel", TC_VARIANTS)
+@pytest.mark.parametrize("dtype,q_scale,k_top", [("bf16", 2.0, 6.0), ("f16", 2.0, 6.0), ("bf16", 6.0, 16.0)])
+def test_tc_large_scores_exercise_the_rescale_paths(kernel, dtype, q_scale, k_top):
+    """Inputs scaled so that row maxima keep growing along the keys.  In the two-tile kernel the accumulator
+    rescale runs; the double-buffered kernel's fixed reference maximum (from key tile 0) becomes too stale -
+    beyond 2^15 for FP16 probabilities at these scales, beyond 2^64 for BF16 at the largest - so its tiles are
+    flagged and recomputed by the second pass."""
     B, H, S, D = 1, 2, 1024, 128
     rng = np.random.default_rng(77)
-    ramp = np.linspace(0.2, 6.0, S, dtype=np.float32)[None, None, :, None]
-    q = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32) * 2, "bf16"), "bf16")
-    k = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32) * ramp, "bf16"), "bf16")
-    v = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32), "bf16"), "bf16")
+    ramp = np.linspace(0.2, k_top, S, dtype=np.float32)[None, None, :, None]
+    q = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32) * q_scale, dtype), dtype)
+    k = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32) * ramp, dtype), dtype)
+    v = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32), dtype), dtype)
     want = o.attention_fwd(q, k, v, 1 / np.sqrt(D), False)
-    tq, tk, tv = (torch.from_numpy(x).to(torch.bfloat16).to(DEV) for x in (q, k, v))
-    out = ops.flash_attention_forward(tq, tk, tv, scale=1 / np.sqrt(D), kernel=abi.KERNEL_TC)
-    u.assert_close(u.torch_to_f32(out), want, "bf16", "growing maxima")
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    tq, tk, tv = (torch.from_numpy(x).to(tdt).to(DEV) for x in (q, k, v))
+    out = ops.flash_attention_forward(tq, tk, tv, scale=1 / np.sqrt(D), kernel=kernel)
+    u.assert_close(u.torch_to_f32(out), want, dtype, "growing maxima")
     assert _error_word() == 0
 
 
@@ -170,9 +181,11 @@ def test_tc_lse():
     B, H, S, D = 1, 2, 300, 64
     (q, k, v), (tq, tk, tv) = u.rounded_inputs((B, H, S, D), "f16", 41)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=DEV)
-    ops.flash_attention_forward(tq.to(DEV), tk.to(DEV), tv.to(DEV), causal=True, lse=lse, kernel=abi.KERNEL_TC)
-    _, want = o.attention_fwd(q, k, v, 1 / np.sqrt(D), True, return_lse=True)
-    assert np.abs(lse.cpu().numpy() - want).max() <= 2e-3
+    for kernel in TC_VARIANTS:
+        lse.zero_()
+        ops.flash_attention_forward(tq.to(DEV), tk.to(DEV), tv.to(DEV), causal=True, lse=lse, kernel=kernel)
+        _, want = o.attention_fwd(q, k, v, 1 / np.sqrt(D), True, return_lse=True)
+        assert np.abs(lse.cpu().numpy() - want).max() <= 2e-3
 
 
 def _full_size_inputs(c):
