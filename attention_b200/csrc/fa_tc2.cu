@@ -38,8 +38,22 @@ namespace {
 using namespace ptx;
 using namespace tc;
 
-constexpr int TC2_THREADS = 352;
-constexpr int S_WARP = 8, O_WARP = 9, LOAD_WARP = 10;
+constexpr int SOFTMAX_WARPS = 16;          // four groups of four warps
+constexpr int TC2_THREADS = (SOFTMAX_WARPS + 4) * 32;   // + the three issuing warps and an idle one that completes their warpgroup
+constexpr int S_WARP = SOFTMAX_WARPS, O_WARP = SOFTMAX_WARPS + 1, LOAD_WARP = SOFTMAX_WARPS + 2;
+// The kernel is launched with 96 registers per thread (65536 / 640 rounded down to a multiple of 8); the issuing
+// warpgroup then hands most of its share to the softmax warpgroups: 512 * 104 + 128 * 40 <= 640 * 96.
+constexpr int SOFTMAX_REGS = 104, ISSUER_REGS = 40;
+// Which of every 8 consecutive score pairs get their 2^x from poly_exp2_x2 (FMA pipe) instead of ex2 (special-
+// function unit, 16 results per clock per SM - as many cycles per key tile as the two tensor-core contractions).
+#ifndef AHPC_TC2_POLY
+#define AHPC_TC2_POLY 0x0
+#endif
+#ifndef AHPC_TC2_PINGPONG
+#define AHPC_TC2_PINGPONG 0
+#endif
+constexpr uint32_t POLY_PATTERN = AHPC_TC2_POLY;
+constexpr bool EXP_TURNS = AHPC_TC2_PINGPONG != 0;
 
 template <int D> struct Cfg2 {
     static constexpr int SUBTILES = D / 64;                  // 64-element (128-byte) wide column blocks
@@ -48,8 +62,8 @@ template <int D> struct Cfg2 {
     static constexpr int RING = D == 128 ? 3 : 6;             // depth of the K ring and of the V ring (tiles each)
     static constexpr int LEAD = 4;                            // S(i + LEAD) is issued right after O += P(i) V(i)
     static constexpr uint32_t SMEM_TILES = (1 + 2 * RING) * TILE_BYTES;
-    static constexpr uint32_t AUX_BYTES = 2048;               // barriers + per-row exchange arrays
-    static constexpr uint32_t SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + AUX_BYTES;
+    static constexpr uint32_t AUX_BYTES = 3072;               // barriers + per-row exchange arrays
+    static constexpr uint32_t SMEM_BYTES = SMEM_TILES + AUX_BYTES;   // 232448 for head_dim 128: all of an SM's shared memory
     static constexpr uint32_t P_COL = 256, O_COL = 384;
 };
 
@@ -86,14 +100,16 @@ struct Tc2Params {
 #define WAITP(slot, ...) ([&] { PROF_T0(); const bool r_ = wait_bounded(__VA_ARGS__); PROF_ADD(slot); return r_; }())
 
 struct Aux2 {            // lives behind the tiles in shared memory
-    uint64_t q, s_full[2], s_free[2], p_full[2], p_free[2], o_done, m_ready, l_ready, k_full[6], k_empty[6], v_full[6], v_empty[6];
+    uint64_t q, s_full[2], s_free[2], p_full[2], p_free[2], o_done, m_ready, m_taken, l_ready, exp_done[2][4];
+    uint64_t k_full[6], k_empty[6], v_full[6], v_empty[6];
     uint32_t tmem_base;
     int abort;
     int redo;
-    float m_ref[BM];      // reference maximum of each row (written by warps 0-3)
-    float l_part[2][BM];  // row sums of the two softmax groups
+    // Row sums of the four softmax groups.  The first two rows of the array first carry the row maxima of key
+    // tile 0 (left and right half of its columns); `m_taken` says that every group has read them.
+    float l_part[4][BM];
 };
-static_assert(sizeof(Aux2) <= 2048, "Aux2 must fit its reserved bytes");
+static_assert(sizeof(Aux2) <= 3072, "Aux2 must fit its reserved bytes");
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(TC2_THREADS, 1)
@@ -103,9 +119,9 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // A tile's partial row sum at or above this means some probability left the range reserved for P
     // (FP16 holds up to 65504; BF16 shares the exponent range of FP32, 2^64 leaves room for the sums).
     constexpr float GROW_SUM_LIMIT = BF16 ? 1.8446744e19f : 32768.0f;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];     // 128-byte-swizzled tiles need 1024-byte alignment
+    const uint32_t smem_base = smem_u32(smem_raw);
+    uint8_t* smem_aligned = smem_raw;
     const uint32_t q_smem = smem_base;
     const uint32_t k_ring = smem_base + C::TILE_BYTES;
     const uint32_t v_ring = k_ring + C::RING * C::TILE_BYTES;
@@ -127,20 +143,23 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         mbar_init(smem_u32(&aux->q), 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&aux->s_full[i]), 1);
-            mbar_init(smem_u32(&aux->s_free[i]), 4);
-            mbar_init(smem_u32(&aux->p_full[i]), 4);
+            mbar_init(smem_u32(&aux->s_free[i]), 8);
+            mbar_init(smem_u32(&aux->p_full[i]), 8);
             mbar_init(smem_u32(&aux->p_free[i]), 1);
         }
         mbar_init(smem_u32(&aux->o_done), 1);
-        mbar_init(smem_u32(&aux->m_ready), 4);
-        mbar_init(smem_u32(&aux->l_ready), 8);
+        mbar_init(smem_u32(&aux->m_ready), 8);
+        mbar_init(smem_u32(&aux->m_taken), SOFTMAX_WARPS);
+        mbar_init(smem_u32(&aux->l_ready), SOFTMAX_WARPS);
+        for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&aux->exp_done[i >> 2][i & 3]), 2);
         for (int s = 0; s < C::RING; ++s) {
             mbar_init(smem_u32(&aux->k_full[s]), 1);
             mbar_init(smem_u32(&aux->k_empty[s]), 1);
             mbar_init(smem_u32(&aux->v_full[s]), 1);
             mbar_init(smem_u32(&aux->v_empty[s]), 1);
         }
-        aux->abort = 0;
+        aux->abort = (smem_base & 1023u) ? 1 : 0;              // misaligned tiles: every role leaves at its first wait
+        if (aux->abort) atomicCAS(p.error_word, 0, 1001);
         aux->redo = 0;
         fence_mbar_init();
     }
@@ -154,7 +173,10 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem = aux->tmem_base;
 
+    // The softmax threads hold a whole score row each; the issuing warpgroup gives them its spare registers.
+    // (Each role's branch starts with its own setmaxnreg so that the register limit follows the role.)
     if (warp == LOAD_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0 && n_kv > 0) {
             prefetch_tensormap(&map_q);
@@ -212,6 +234,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
         }
     } else if (warp == S_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
         // ------------------------------------------------------------------ issuer of S = Q K^T
         if (lane == 0 && n_kv > 0) {
             constexpr uint32_t IDESC_S = idesc_f16(BF16 ? 1 : 0, BM, BN, 0, 0);     // Q (K-major) x K (K-major)
@@ -248,6 +271,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             PROF_FLUSH(8);
         }
     } else if (warp == O_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
         // ------------------------------------------------------------------ issuer of O += P V
         if (lane == 0 && n_kv > 0) {
             constexpr uint32_t IDESC_O = idesc_f16(BF16 ? 1 : 0, BM, D, 0, 1);      // P (TMEM) x V (MN-major)
@@ -280,22 +304,29 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #endif
             PROF_FLUSH(24);
         }
+    } else if (warp > LOAD_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
-        const int g = warp >> 2;                               // softmax group: key tiles j = g, g+2, ...
-        const int r_in_tile = (warp & 3) * 32 + lane;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SOFTMAX_REGS));
+        // Four groups of four warps.  Group wg works on the key tiles of parity g = wg & 1 and, of each such tile,
+        // on the 64 columns of half hc = wg >> 1; warp w of every group owns the TMEM lanes (query rows) 32 w .. 32 w + 31,
+        // one thread per row.  So each scheduler (4 warps sharing the same rows) always has two warps in their
+        // exponentials while the other two wait, load or store.
+        const int wg = warp >> 2, g = wg & 1, hc = wg >> 1, quad = warp & 3;
+        const int r_in_tile = quad * 32 + lane;
         const int row = q0 + r_in_tile;
-        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t s_addr = tmem + lane_base + g * BN;
-        const uint32_t p_addr = tmem + lane_base + C::P_COL + g * 64;
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const uint32_t s_addr = tmem + lane_base + g * BN + hc * 64;
+        const uint32_t p_addr = tmem + lane_base + C::P_COL + g * 64 + hc * 32;
         const uint32_t o_addr = tmem + lane_base + C::O_COL;
         float m_ref = 0.f, l_run = 0.f;
-        bool ok = true, grew = false;
+        bool ok = true, grew = false, took_m = false;
         PROF_DECL();
         const long long prof_start = clock64();
 
         int i = 0;
-        const bool tracer = (warp & 3) == 0 && lane == 0;
+        const bool tracer = quad == 0 && hc == 0 && lane == 0;
         (void)tracer;
         const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
         for (int j = g; j < n_kv; j += 2, ++i) {
@@ -305,90 +336,88 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tc_fence_after_sync();
             if (tracer) TRACE(3 + g, j, 1);
 
-            const int k0 = j * BN;
-            const bool need_mask = (p.causal && k0 + BN - 1 > q0) || (k0 + BN > p.seq_kv);
+            const int k0 = j * BN + hc * 64;                                            // first key of this warp's columns
+            const bool need_mask = (p.causal && j * BN + BN - 1 > q0) || (j * BN + BN > p.seq_kv);
             const int limit = p.causal ? min(p.seq_kv - 1, row) : p.seq_kv - 1;         // last visible key
-            uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};                                // four packed partial row sums
-            uint32_t packed[4][16];
-            uint64_t negm2 = 0ull;
-            // 32 scores of the row -> probabilities (16 packed pairs) and their contribution to the row sum
-            auto process = [&](uint32_t (&sr)[32], int c) {
-                if (need_mask) {
+            uint32_t sr[2][32];
+            tmem_ld32(s_addr, sr[0]);
+            tmem_ld32(s_addr + 32, sr[1]);
+            tmem_wait_ld();
+            // this warp's copy of its part of S[g] is complete: the buffer may take the tile after next
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->s_free[g]));
+            if (tracer) TRACE(3 + g, j, 2);
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
 #pragma unroll
                     for (int e = 0; e < 32; ++e)
-                        if (k0 + c * 32 + e > limit) sr[e] = 0xff800000u;               // -inf
-                }
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const uint64_t x2 = fma2(pack_u2(sr[2 * e], sr[2 * e + 1]), scale2, negm2);
-                    const float p0 = fast_exp2(__uint_as_float((uint32_t)x2));
-                    const float p1 = fast_exp2(__uint_as_float((uint32_t)(x2 >> 32)));
-                    sum2[e & 3] = add2(sum2[e & 3], pack_f2(p0, p1));
-                    packed[c][e] = pack2<BF16>(p0, p1);
-                }
-            };
-            auto release_s = [&] {      // this warp's copy of S[g] is complete: the buffer may take the next tile
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&aux->s_free[g]));
-            };
-
+                        if (k0 + c * 32 + e > limit) sr[c][e] = 0xff800000u;            // -inf
+            }
             if (j == 0) {
-                // Key tile 0 fixes the reference maximum of the row for both groups: it needs the whole row first.
-                uint32_t sr[4][32];
+                // Key tile 0 fixes the reference maximum of the row for all groups: the two halves meet in shared memory.
+                float mx[2];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr[c]);
-                tmem_wait_ld();
-                release_s();
-                float mx[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 2; ++c) {
                     mx[c] = -INFINITY;
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const float s0 = (!need_mask || k0 + c * 32 + e <= limit) ? __uint_as_float(sr[c][e]) : -INFINITY;
-                        const float s1 = (!need_mask || k0 + c * 32 + e + 1 <= limit) ? __uint_as_float(sr[c][e + 1]) : -INFINITY;
-                        mx[c] = max3(mx[c], s0, s1);
-                    }
+                    for (int e = 0; e < 32; e += 2) mx[c] = max3(mx[c], __uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
                 }
-                m_ref = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-                if (n_kv > 1) {
-                    aux->m_ref[r_in_tile] = m_ref;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&aux->m_ready));
-                }
-                negm2 = pack_f2(-m_ref * p.scale_log2, -m_ref * p.scale_log2);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) process(sr[c], c);
-            } else {
-                if (i == 0) {      // group 1 at its first tile
-                    ok = WAITP(2, smem_u32(&aux->m_ready), 0, abort_flag, p.error_word, 1320);
-                    if (!ok) break;
-                    m_ref = aux->m_ref[r_in_tile];
-                }
-                negm2 = pack_f2(-m_ref * p.scale_log2, -m_ref * p.scale_log2);
-                // No row maximum is needed here.  The whole row is copied out first so that S[g] can take the
-                // tile after next while this one is exponentiated.
-                uint32_t sr[4][32];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr[c]);
-                tmem_wait_ld();
-                release_s();
-                if (tracer) TRACE(3 + g, j, 2);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) process(sr[c], c);
+                aux->l_part[hc][r_in_tile] = fmaxf(mx[0], mx[1]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&aux->m_ready));
             }
-            if (tracer) TRACE(3 + g, j, 4);
-            if (i >= 1) {          // P[g] may still feed the PV MMA of this group's previous tile
+            if (i == 0) {
+                ok = WAITP(2, smem_u32(&aux->m_ready), 0, abort_flag, p.error_word, 1320);
+                if (!ok) break;
+                m_ref = fmaxf(aux->l_part[0][r_in_tile], aux->l_part[1][r_in_tile]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&aux->m_taken));
+                took_m = true;
+            }
+            if (i >= 1) {          // P[g] may still feed the PV MMA of this parity's previous tile (normally long done)
                 ok = WAITP(1, smem_u32(&aux->p_free[g]), (i - 1) & 1, abort_flag, p.error_word, 1330 + g);
                 if (!ok) break;
                 tc_fence_after_sync();
             }
-            if (tracer) TRACE(3 + g, j, 5);
+            uint64_t negm2 = pack_f2(-m_ref * p.scale_log2, -m_ref * p.scale_log2);
+            if (EXP_TURNS && j >= 1) {
+                // The exponentials of consecutive key tiles take turns on each scheduler's special-function unit.
+                ok = WAITP(5, smem_u32(&aux->exp_done[g ^ 1][quad]), ((j - 1) >> 1) & 1, abort_flag, p.error_word, 1360 + g);
+                if (!ok) break;
+                asm volatile("" : "+l"(negm2));          // the exponentials below stay behind the wait
+            }
+            if (tracer) TRACE(3 + g, j, 3);
+            uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};                                // four packed partial row sums
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_st16(p_addr + c * 16, packed[c]);
+            for (int c = 0; c < 2; ++c) {
+                // In three passes (arguments, exponentials, sums and packing), so that the warp issues a run of
+                // independent ex2 before the first instruction that needs one of their results.
+                uint64_t x2[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) x2[e] = fma2(pack_u2(sr[c][2 * e], sr[c][2 * e + 1]), scale2, negm2);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    if ((POLY_PATTERN >> (e & 7)) & 1u) {
+                        x2[e] = poly_exp2_x2(x2[e]);
+                    } else {
+                        x2[e] = pack_f2(fast_exp2(__uint_as_float((uint32_t)x2[e])), fast_exp2(__uint_as_float((uint32_t)(x2[e] >> 32))));
+                    }
+                }
+                uint32_t packed[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    sum2[e & 3] = add2(sum2[e & 3], x2[e]);
+                    packed[e] = pack2<BF16>(__uint_as_float((uint32_t)x2[e]), __uint_as_float((uint32_t)(x2[e] >> 32)));
+                }
+                tmem_st16(p_addr + c * 16, packed);
+            }
             const uint64_t tot = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
             const float psum = __uint_as_float((uint32_t)tot) + __uint_as_float((uint32_t)(tot >> 32));
+            // the arrival takes the row sum as an operand, which keeps it behind the last exponential
+            if (EXP_TURNS && lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&aux->exp_done[g][quad])), "f"(psum) : "memory");
+            if (tracer) TRACE(3 + g, j, 4);
             // A probability beyond the range reserved for P means the reference maximum is too stale for this row.
             grew |= !(psum < GROW_SUM_LIMIT);
             l_run += psum;
@@ -403,36 +432,41 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         prof_acc[3] = clock64() - prof_start;
 #endif
 
-        // row sums of both groups meet in shared memory; then each group stores half of the columns
-        aux->l_part[g][r_in_tile] = l_run;
+        // The row sums of the four groups meet in shared memory, in the array that carried the maxima of key tile 0:
+        // first make sure every group has taken those.
+        if (!took_m) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->m_taken));
+        }
+        if (ok) ok = WAITP(4, smem_u32(&aux->m_taken), 0, abort_flag, p.error_word, 1335);
+        if (ok) aux->l_part[wg][r_in_tile] = l_run;
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&aux->l_ready));
-        if (ok && n_kv > 0) ok = WAITP(4, smem_u32(&aux->l_ready), 0, abort_flag, p.error_word, 1340);
-        if (ok && n_kv > 0) ok = WAITP(4, smem_u32(&aux->o_done), 0, abort_flag, p.error_word, 1350);
-        if (ok && n_kv > 0) {
+        if (ok) ok = WAITP(4, smem_u32(&aux->l_ready), 0, abort_flag, p.error_word, 1340);
+        if (ok) ok = WAITP(4, smem_u32(&aux->o_done), 0, abort_flag, p.error_word, 1350);
+        if (ok) {
+            // each group stores a quarter of the columns of O
             tc_fence_after_sync();
-            const float l_tot = aux->l_part[0][r_in_tile] + aux->l_part[1][r_in_tile];
+            const float l_tot = (aux->l_part[0][r_in_tile] + aux->l_part[1][r_in_tile]) + (aux->l_part[2][r_in_tile] + aux->l_part[3][r_in_tile]);
             const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            constexpr int HALF = D / 2;
-            uint16_t* orow_g = static_cast<uint16_t*>(p.out) + b * p.os[0] + h * p.os[1] + (long long)row * p.os[2] + g * HALF;
+            constexpr int QUART = D / 4;
+            uint16_t* orow_g = static_cast<uint16_t*>(p.out) + b * p.os[0] + h * p.os[1] + (long long)row * p.os[2] + wg * QUART;
+            uint32_t orow[QUART];
+            if constexpr (QUART == 32) tmem_ld32(o_addr + wg * QUART, orow);      // warp-collective: rows past seq_q still take part
+            else tmem_ld16(o_addr + wg * QUART, orow);
+            tmem_wait_ld();
+            if (row < p.seq_q) {
 #pragma unroll
-            for (int c = 0; c < HALF / 32; ++c) {
-                uint32_t orow[32];
-                tmem_ld32(o_addr + g * HALF + c * 32, orow);      // warp-collective: rows past seq_q still take part
-                tmem_wait_ld();
-                if (row < p.seq_q) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        uint4 v;
-                        v.x = pack2<BF16>(__uint_as_float(orow[8 * e + 0]) * inv, __uint_as_float(orow[8 * e + 1]) * inv);
-                        v.y = pack2<BF16>(__uint_as_float(orow[8 * e + 2]) * inv, __uint_as_float(orow[8 * e + 3]) * inv);
-                        v.z = pack2<BF16>(__uint_as_float(orow[8 * e + 4]) * inv, __uint_as_float(orow[8 * e + 5]) * inv);
-                        v.w = pack2<BF16>(__uint_as_float(orow[8 * e + 6]) * inv, __uint_as_float(orow[8 * e + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow_g + c * 32 + e * 8) = v;
-                    }
+                for (int e = 0; e < QUART / 8; ++e) {
+                    uint4 v;
+                    v.x = pack2<BF16>(__uint_as_float(orow[8 * e + 0]) * inv, __uint_as_float(orow[8 * e + 1]) * inv);
+                    v.y = pack2<BF16>(__uint_as_float(orow[8 * e + 2]) * inv, __uint_as_float(orow[8 * e + 3]) * inv);
+                    v.z = pack2<BF16>(__uint_as_float(orow[8 * e + 4]) * inv, __uint_as_float(orow[8 * e + 5]) * inv);
+                    v.w = pack2<BF16>(__uint_as_float(orow[8 * e + 6]) * inv, __uint_as_float(orow[8 * e + 7]) * inv);
+                    *reinterpret_cast<uint4*>(orow_g + e * 8) = v;
                 }
             }
-            if (g == 0 && p.lse && row < p.seq_q)
+            if (wg == 0 && p.lse && row < p.seq_q)
                 p.lse[((long long)b * p.heads + h) * p.seq_q + row] = l_tot > 0.f ? m_ref * p.scale + logf(l_tot) : -INFINITY;
         }
 #ifdef AHPC_TC2_PROF
