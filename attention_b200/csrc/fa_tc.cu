@@ -25,6 +25,7 @@
 // Every wait in this kernel is bounded: when a barrier does not complete within the limit the
 // waiting thread records a code in a global error word, raises a CTA-wide abort flag, and every
 // role leaves its loop; tensor memory is then released and the kernel returns.
+#include <algorithm>
 #include <map>
 #include <mutex>
 
@@ -55,8 +56,9 @@ struct TcParams {
     int causal;
     int n_pairs;
     int* error_word;
-    const int* redo;     // when set: per 128-row tile flags [tile][batch*heads]; only flagged pairs are computed
+    const int* redo;     // when set: per 128-row tile flags [batch*heads][tile slot]; only flagged pairs are computed
     int n_tiles;
+    int* item_counter;   // when set: the item counter of the preceding fa_fwd_tc2_kernel launch, put back to zero here
 };
 
 struct Barriers {        // one uint64 each, in shared memory
@@ -80,39 +82,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // Which (pair of query tiles, batch, head).  Consecutive CTAs are the pairs of ONE (batch, head), so the CTAs
-    // resident at any time share a few K/V streams and those stay in L2; heavy (late) pairs first when causal.
-    const int bh_count = p.batch * p.heads;
-    const int bh = blockIdx.x / p.n_pairs, pair_slot = blockIdx.x % p.n_pairs;
-    const int pair = p.causal ? p.n_pairs - 1 - pair_slot : pair_slot;
-    const int b = bh / p.heads, h = bh % p.heads;
-    const int q0 = pair * 2 * BM;
-    const int n_t0 = kv_tiles_for(q0, p.seq_q, p.seq_kv, p.causal);
-    const int n_t1 = kv_tiles_for(q0 + BM, p.seq_q, p.seq_kv, p.causal);
-    const int n_kv = max(n_t0, n_t1);
-
-    if (p.redo) {
-        // second pass behind fa_fwd_tc2_kernel: only the tiles that kernel flagged are recomputed
-        const int t0 = 2 * pair;
-        const bool wanted = p.redo[(long long)t0 * bh_count + bh] != 0 ||
-                            (t0 + 1 < p.n_tiles && p.redo[(long long)(t0 + 1) * bh_count + bh] != 0);
-        if (!wanted) return;
-    }
-
-    if (threadIdx.x == MMA_WARP * 32) {
-        for (int t = 0; t < 2; ++t) {
-            mbar_init(smem_u32(&bars->q[t]), 1);
-            mbar_init(smem_u32(&bars->s[t]), 1);
-            mbar_init(smem_u32(&bars->p[t]), BM);
-            mbar_init(smem_u32(&bars->o[t]), 1);
-        }
-        for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(smem_u32(&bars->full[s]), 1);
-            mbar_init(smem_u32(&bars->empty[s]), 1);
-        }
-        bars->abort = 0;
-        fence_mbar_init();
-    }
+    if (threadIdx.x == MMA_WARP * 32) bars->abort = 0;
     if (warp == MMA_WARP) {
         __syncwarp();
         tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLS);
@@ -122,6 +92,49 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = bars->tmem_base;
+    if (p.redo && blockIdx.x == 0 && threadIdx.x == 0 && p.item_counter) *p.item_counter = 0;
+
+    // Work = one pair of query tiles of one (batch, head).  Launched on its own, every CTA has exactly one pair.  As the
+    // second pass behind fa_fwd_tc2_kernel (p.redo set) the grid is one CTA per SM and a CTA walks, with the grid's
+    // stride, through the pairs of which that kernel flagged a tile: normally none, and the kernel ends at once.
+    const int total_pairs = p.n_pairs * p.batch * p.heads;
+    bool first_round = true;
+    for (int work = blockIdx.x;; work += gridDim.x, first_round = false) {
+        if (p.redo) {
+            for (; work < total_pairs; work += gridDim.x) {
+                const int bh_w = work / p.n_pairs, slot_w = work % p.n_pairs;
+                const int t0 = 2 * (p.causal ? p.n_pairs - 1 - slot_w : slot_w);
+                const int slot0 = p.causal ? p.n_tiles - 1 - t0 : t0, slot1 = p.causal ? slot0 - 1 : slot0 + 1;   // fa_fwd_tc2_kernel's item order
+                if (p.redo[(long long)bh_w * p.n_tiles + slot0] != 0 || (t0 + 1 < p.n_tiles && p.redo[(long long)bh_w * p.n_tiles + slot1] != 0)) break;
+            }
+        }
+        if (work >= total_pairs) break;
+    // Consecutive work numbers are the pairs of ONE (batch, head), so the CTAs resident at any time share a few K/V
+    // streams and those stay in L2; heavy (late) pairs first when causal.
+    const int bh = work / p.n_pairs, pair_slot = work % p.n_pairs;
+    const int pair = p.causal ? p.n_pairs - 1 - pair_slot : pair_slot;
+    const int b = bh / p.heads, h = bh % p.heads;
+    const int q0 = pair * 2 * BM;
+    const int n_t0 = kv_tiles_for(q0, p.seq_q, p.seq_kv, p.causal);
+    const int n_t1 = kv_tiles_for(q0 + BM, p.seq_q, p.seq_kv, p.causal);
+    const int n_kv = max(n_t0, n_t1);
+
+    if (threadIdx.x == MMA_WARP * 32) {
+        for (int t = 0; t < 2; ++t) {
+            if (!first_round) { mbar_inval(smem_u32(&bars->q[t])); mbar_inval(smem_u32(&bars->s[t])); mbar_inval(smem_u32(&bars->p[t])); mbar_inval(smem_u32(&bars->o[t])); }
+            mbar_init(smem_u32(&bars->q[t]), 1);
+            mbar_init(smem_u32(&bars->s[t]), 1);
+            mbar_init(smem_u32(&bars->p[t]), BM);
+            mbar_init(smem_u32(&bars->o[t]), 1);
+        }
+        for (int s = 0; s < C::STAGES; ++s) {
+            if (!first_round) { mbar_inval(smem_u32(&bars->full[s])); mbar_inval(smem_u32(&bars->empty[s])); }
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
 
     if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer
@@ -214,6 +227,12 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     tc_commit(smem_u32(&bars->empty[slot_v]));
                     if (more) tc_commit(smem_u32(&bars->empty[slot_k]));
                 }
+            }
+            // The last commit has nobody waiting for it; see it land before the barriers may be set up again for
+            // another pair (commits complete in order, so this covers the earlier ones too).
+            if (ok && p.redo) {
+                const int idx_last = 2 * (n_kv - 1) + 1;
+                ok = wait_bounded(smem_u32(&bars->empty[idx_last % C::STAGES]), (idx_last / C::STAGES) & 1, abort_flag, p.error_word, 250);
             }
         }
     } else {
@@ -338,10 +357,11 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == MMA_WARP) {
-        tc_fence_after_sync();
-        tmem_dealloc(tmem, TMEM_COLS);
-    }
+    tc_fence_after_sync();
+        if (!p.redo || bars->abort) break;
+    }   // work loop
+
+    if (warp == MMA_WARP) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 template <int D, bool BF16>
@@ -349,7 +369,8 @@ ahpc_status launch(const FaLaunch& a, const CUtensorMap& mq, const CUtensorMap& 
     using C = Cfg<D>;
     auto kernel = fa_fwd_tc_kernel<D, BF16>;
     AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
-    const long long ctas = (long long)p.n_pairs * a.batch * a.heads;
+    long long ctas = (long long)p.n_pairs * a.batch * a.heads;
+    if (p.redo) ctas = std::min<long long>(ctas, std::max(1, sm_count(a.device)));      // second pass: one CTA per SM walks the flags
     kernel<<<(unsigned)ctas, TC_THREADS, C::SMEM_BYTES, a.stream>>>(mq, mk, mv, p);
     AHPC_CUDA_OK(cudaGetLastError());
     return AHPC_SUCCESS;
@@ -451,30 +472,41 @@ namespace {
 // a per-device ring, so launches in flight on different streams do not share flags until the ring
 // (1 Mi entries) has wrapped completely.
 constexpr long long REDO_RING_ENTRIES = 1ll << 20;
+constexpr int ITEM_COUNTERS = 1024;       // item counters of fa_fwd_tc2_kernel launches, handed out in turn
+struct RedoRingState {
+    int* flags = nullptr;
+    int* counters = nullptr;
+    long long cursor = 0;
+    int next_counter = 0;
+};
 struct RedoRing {
     std::mutex mu;
-    std::map<int, std::pair<int*, long long>> per_device;   // base, cursor
+    std::map<int, RedoRingState> per_device;
 };
 RedoRing& redo_ring() {
     static RedoRing r;
     return r;
 }
-ahpc_status redo_flags_for(int device, long long n, int** out) {
+// A range of n flags and one zeroed item counter for a launch on `device`.  A counter is zero when handed out:
+// they start zeroed and the second-pass kernel of the launch that used one puts it back.
+ahpc_status redo_flags_for(int device, long long n, int** flags, int** counter) {
     RedoRing& r = redo_ring();
     std::lock_guard<std::mutex> lock(r.mu);
-    auto it = r.per_device.find(device);
-    if (it == r.per_device.end()) {
-        int* base = nullptr;
-        AHPC_CUDA_OK(cudaMalloc(&base, REDO_RING_ENTRIES * sizeof(int)));
-        it = r.per_device.emplace(device, std::make_pair(base, 0ll)).first;
+    RedoRingState& st = r.per_device[device];
+    if (!st.flags) {
+        AHPC_CUDA_OK(cudaMalloc(&st.flags, REDO_RING_ENTRIES * sizeof(int)));
+        AHPC_CUDA_OK(cudaMalloc(&st.counters, ITEM_COUNTERS * sizeof(int)));
+        AHPC_CUDA_OK(cudaMemset(st.counters, 0, ITEM_COUNTERS * sizeof(int)));
     }
-    if (it->second.second + n > REDO_RING_ENTRIES) it->second.second = 0;
-    *out = it->second.first + it->second.second;
-    it->second.second += n;
+    if (st.cursor + n > REDO_RING_ENTRIES) st.cursor = 0;
+    *flags = st.flags + st.cursor;
+    st.cursor += n;
+    *counter = st.counters + st.next_counter;
+    st.next_counter = (st.next_counter + 1) % ITEM_COUNTERS;
     return AHPC_SUCCESS;
 }
 
-ahpc_status launch_two_tile(const FaLaunch& a, const int* redo) {
+ahpc_status launch_two_tile(const FaLaunch& a, const int* redo, int* item_counter) {
     CUtensorMap mq, mk, mv;
     AHPC_TRY(make_map(&mq, a.q, a.dtype, a.batch, a.heads, a.seq_q, a.head_dim, a.qs));
     AHPC_TRY(make_map(&mk, a.k, a.dtype, a.batch, a.heads, a.seq_kv, a.head_dim, a.ks));
@@ -489,6 +521,7 @@ ahpc_status launch_two_tile(const FaLaunch& a, const int* redo) {
     p.n_pairs = (a.seq_q + 2 * BM - 1) / (2 * BM);
     p.n_tiles = (a.seq_q + BM - 1) / BM;
     p.redo = redo;
+    p.item_counter = item_counter;
     AHPC_TRY(error_word_for(a.device, &p.error_word));
     const bool bf16 = a.dtype == AHPC_BF16;
     if (a.head_dim == 128) return bf16 ? launch<128, true>(a, mq, mk, mv, p) : launch<128, false>(a, mq, mk, mv, p);
@@ -501,13 +534,17 @@ ahpc_status launch_fa_tc(const FaLaunch& a, int variant) {
     const char* why = nullptr;
     if (!fa_tc_supported(a, &why)) return fail(AHPC_UNSUPPORTED_OPERATION, "tensor-core kernel not applicable: %s", why);
     const long long tiles = (long long)((a.seq_q + BM - 1) / BM) * a.batch * a.heads;
+    // The library's own choice (AHPC_FA_KERNEL_TC): the persistent double-buffered kernel for BF16, whose probabilities
+    // have the exponent range of FP32, so its second pass has practically never anything to do; the two-tile kernel
+    // for FP16, where scores that outgrow key tile 0's maximum by 2^15 would send tiles through both kernels.
+    if (variant == AHPC_FA_KERNEL_TC) variant = a.dtype == AHPC_BF16 ? AHPC_FA_KERNEL_TC_DOUBLE_S : AHPC_FA_KERNEL_TC_TWO_TILE;
     if (variant != AHPC_FA_KERNEL_TC_DOUBLE_S || tiles > REDO_RING_ENTRIES || tiles > 2147483647ll)
-        return launch_two_tile(a, nullptr);
+        return launch_two_tile(a, nullptr, nullptr);
     // double-buffered-score kernel, then the two-tile kernel over the tiles it flagged (normally none)
-    int* redo = nullptr;
-    AHPC_TRY(redo_flags_for(a.device, tiles, &redo));
-    AHPC_TRY(launch_fa_tc2(a, redo));
-    return launch_two_tile(a, redo);
+    int *redo = nullptr, *counter = nullptr;
+    AHPC_TRY(redo_flags_for(a.device, tiles, &redo, &counter));
+    AHPC_TRY(launch_fa_tc2(a, redo, counter));
+    return launch_two_tile(a, redo, counter);
 }
 
 // Non-zero when a kernel of this file gave up on a wait since the last call (synchronises the device).
