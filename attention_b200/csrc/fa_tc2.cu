@@ -18,6 +18,7 @@
 //               one overlap the MMAs of the other, so the tensor pipe is not idle while a thread waits)
 //   warp  18    lane 0 issues the TMA loads (Q per item, K and V tiles through two rings)
 //   warp  19    lane 0 draws the next items from the global counter, two ahead of the other roles
+//   warps 20-23 epilogue: O / row sum -> global memory, while the softmax warps are already on the next item
 //
 // Because P has its own columns, a score buffer is free again as soon as its softmax warps have
 // copied it to registers, and no softmax step waits for an MMA that depends on its own output: the
@@ -46,11 +47,12 @@ using namespace ptx;
 using namespace tc;
 
 constexpr int SOFTMAX_WARPS = 16;          // four groups of four warps
-constexpr int TC2_THREADS = (SOFTMAX_WARPS + 4) * 32;
+constexpr int TC2_THREADS = (SOFTMAX_WARPS + 8) * 32;
 constexpr int S_WARP = SOFTMAX_WARPS, O_WARP = SOFTMAX_WARPS + 1, LOAD_WARP = SOFTMAX_WARPS + 2, SCHED_WARP = SOFTMAX_WARPS + 3;
-// The kernel is launched with 96 registers per thread (65536 / 640 rounded down to a multiple of 8); the issuing
-// warpgroup then hands most of its share to the softmax warpgroups: 512 * 104 + 128 * 40 <= 640 * 96.
-constexpr int SOFTMAX_REGS = 104, ISSUER_REGS = 40;
+constexpr int EPI_WARP0 = SOFTMAX_WARPS + 4;          // four epilogue warps (a warpgroup: warp EPI_WARP0 + q owns TMEM lanes 32 q ..)
+// The kernel is launched with 80 registers per thread (65536 / 768 rounded down to a multiple of 8); the issuing and
+// epilogue warpgroups then hand part of their share to the softmax warpgroups: 512 * 96 + 256 * 48 = 768 * 80.
+constexpr int SOFTMAX_REGS = 96, OTHER_REGS = 48;
 // Which of every 8 consecutive score pairs get their 2^x from poly_exp2_x2 (FMA pipe) instead of ex2 (special-
 // function unit).  Measured on B200: no pattern beats all-ex2 (the packed FP32 instructions of the cubic cost the
 // FMA pipe about as many cycles as the ex2 they replace cost the special-function unit), so the default is none.
@@ -92,6 +94,7 @@ struct Aux2 {            // lives behind the tiles in shared memory
     uint32_t tmem_base;
     int abort;
     int item[2];         // the scheduler's two-entry queue of item numbers (-1: no more)
+    float m_ref[BM];     // reference maximum of each row of the current item, for the log-sum-exp output
     // Row sums of the four softmax groups.  The first two rows of the array first carry the row maxima of an
     // item's key tile 0 (left and right half of its columns); `m_taken` says that every group has read them,
     // `l_taken` that every group has read the sums (so that the next item's maxima may overwrite them).
@@ -126,14 +129,14 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             mbar_init(smem_u32(&aux->p_full[i]), 8);
             mbar_init(smem_u32(&aux->p_free[i]), 1);
             mbar_init(smem_u32(&aux->item_full[i]), 1);
-            mbar_init(smem_u32(&aux->item_empty[i]), 3 + SOFTMAX_WARPS);
+            mbar_init(smem_u32(&aux->item_empty[i]), 3 + SOFTMAX_WARPS + 4);
         }
         mbar_init(smem_u32(&aux->o_done), 1);
-        mbar_init(smem_u32(&aux->o_free), SOFTMAX_WARPS);
+        mbar_init(smem_u32(&aux->o_free), 4);
         mbar_init(smem_u32(&aux->m_ready), 8);
         mbar_init(smem_u32(&aux->m_taken), SOFTMAX_WARPS);
         mbar_init(smem_u32(&aux->l_ready), SOFTMAX_WARPS);
-        mbar_init(smem_u32(&aux->l_taken), SOFTMAX_WARPS);
+        mbar_init(smem_u32(&aux->l_taken), 4);
         for (int s = 0; s < C::RING; ++s) {
             mbar_init(smem_u32(&aux->k_full[s]), 1);
             mbar_init(smem_u32(&aux->k_empty[s]), 1);
@@ -182,7 +185,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // The softmax threads hold their part of a score row in registers; the issuing warpgroup gives them its spare
     // registers.  (Each role's branch starts with its own setmaxnreg so that the register limit follows the role.)
     if (warp == SCHED_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
         // ------------------------------------------------------------------ item scheduler
         if (lane == 0) {
             for (int k = 0;; ++k) {
@@ -195,7 +198,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
         }
     } else if (warp == LOAD_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             prefetch_tensormap(&map_q);
@@ -257,7 +260,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
         }
     } else if (warp == S_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
         // ------------------------------------------------------------------ issuer of S = Q K^T
         if (lane == 0) {
             constexpr uint32_t IDESC_S = idesc_f16(BF16 ? 1 : 0, BM, BN, 0, 0);     // Q (K-major) x K (K-major)
@@ -290,7 +293,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
         }
     } else if (warp == O_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ISSUER_REGS));
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
         // ------------------------------------------------------------------ issuer of O += P V
         if (lane == 0) {
             constexpr uint32_t IDESC_O = idesc_f16(BF16 ? 1 : 0, BM, D, 0, 1);      // P (TMEM) x V (MN-major)
@@ -320,15 +323,62 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 if (ok) tc_commit(smem_u32(&aux->o_done));
             }
         }
+    } else if (warp >= EPI_WARP0) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
+        // ------------------------------------------------------------------ epilogue: out = O / row sum
+        const int quad = warp & 3;
+        const int r_in_tile = quad * 32 + lane;
+        const uint32_t o_addr = tmem + ((uint32_t)(quad * 32) << 16) + C::O_COL;
+        bool ok = true;
+        for (int k = 0; ok; ++k) {
+            const int w = next_item(k, 1450, true);
+            if (w < 0) break;
+            const Item it = decode(w);
+            const int row = it.q0 + r_in_tile;
+            ok = wait_bounded(smem_u32(&aux->l_ready), k & 1, abort_flag, p.error_word, 1340);
+            if (!ok) break;
+            const float l_tot = (aux->l_part[0][r_in_tile] + aux->l_part[1][r_in_tile]) + (aux->l_part[2][r_in_tile] + aux->l_part[3][r_in_tile]);
+            const float m_ref = aux->m_ref[r_in_tile];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->l_taken));     // the next item's maxima may overwrite the sums
+            ok = wait_bounded(smem_u32(&aux->o_done), k & 1, abort_flag, p.error_word, 1350);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+            uint16_t* orow_g = static_cast<uint16_t*>(p.out) + it.b * p.os[0] + it.h * p.os[1] + (long long)row * p.os[2];
+#pragma unroll 1
+            for (int c = 0; c < D / 16; ++c) {
+                uint32_t orow[16];
+                tmem_ld16(o_addr + c * 16, orow);                 // warp-collective: rows past seq_q still take part
+                tmem_wait_ld();
+                if (c == D / 16 - 1) {                            // O is in registers or memory: it may take the next item
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&aux->o_free));
+                }
+                if (row < p.seq_q) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        uint4 v;
+                        v.x = pack2<BF16>(__uint_as_float(orow[8 * e + 0]) * inv, __uint_as_float(orow[8 * e + 1]) * inv);
+                        v.y = pack2<BF16>(__uint_as_float(orow[8 * e + 2]) * inv, __uint_as_float(orow[8 * e + 3]) * inv);
+                        v.z = pack2<BF16>(__uint_as_float(orow[8 * e + 4]) * inv, __uint_as_float(orow[8 * e + 5]) * inv);
+                        v.w = pack2<BF16>(__uint_as_float(orow[8 * e + 6]) * inv, __uint_as_float(orow[8 * e + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow_g + c * 16 + e * 8) = v;
+                    }
+                }
+            }
+            if (p.lse && row < p.seq_q)
+                p.lse[((long long)it.b * p.heads + it.h) * p.seq_q + row] = l_tot > 0.f ? m_ref * p.scale + logf(l_tot) : -INFINITY;
+        }
     } else {
-        // ------------------------------------------------------------------ softmax + epilogue
+        // ------------------------------------------------------------------ softmax
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SOFTMAX_REGS));
         const int wg = warp >> 2, g = wg & 1, hc = wg >> 1, quad = warp & 3;
         const int r_in_tile = quad * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const uint32_t s_addr = tmem + lane_base + g * BN + hc * 64;
         const uint32_t p_addr = tmem + lane_base + C::P_COL + g * 64 + hc * 32;
-        const uint32_t o_addr = tmem + lane_base + C::O_COL;
         const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
         bool ok = true;
         int t_base = 0;          // key tiles of all earlier items
@@ -386,6 +436,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     ok = wait_bounded(smem_u32(&aux->m_ready), k & 1, abort_flag, p.error_word, 1320);
                     if (!ok) break;
                     m_ref = fmaxf(aux->l_part[0][r_in_tile], aux->l_part[1][r_in_tile]);
+                    if (hc == 0 && g == first_parity) aux->m_ref[r_in_tile] = m_ref;      // for the epilogue warps (log-sum-exp)
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&aux->m_taken));
                     have_m = true;
@@ -437,40 +488,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (grew) p.redo[w] = 1;           // behind warp 0's "0" of this item: the wait above orders the two stores
             aux->l_part[wg][r_in_tile] = l_run;
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&aux->l_ready));
-            ok = wait_bounded(smem_u32(&aux->l_ready), k & 1, abort_flag, p.error_word, 1340);
-            if (!ok) break;
-            const float l_tot = (aux->l_part[0][r_in_tile] + aux->l_part[1][r_in_tile]) + (aux->l_part[2][r_in_tile] + aux->l_part[3][r_in_tile]);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&aux->l_taken));
-            ok = wait_bounded(smem_u32(&aux->o_done), k & 1, abort_flag, p.error_word, 1350);
-            if (!ok) break;
-            // each group stores a quarter of the columns of O
-            tc_fence_after_sync();
-            constexpr int QUART = D / 4;
-            uint32_t orow[QUART];
-            if constexpr (QUART == 32) tmem_ld32(o_addr + wg * QUART, orow);      // warp-collective: rows past seq_q still take part
-            else tmem_ld16(o_addr + wg * QUART, orow);
-            tmem_wait_ld();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&aux->o_free));                   // O may take the next item
-            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            if (row < p.seq_q) {
-                uint16_t* orow_g = static_cast<uint16_t*>(p.out) + it.b * p.os[0] + it.h * p.os[1] + (long long)row * p.os[2] + wg * QUART;
-#pragma unroll
-                for (int e = 0; e < QUART / 8; ++e) {
-                    uint4 v;
-                    v.x = pack2<BF16>(__uint_as_float(orow[8 * e + 0]) * inv, __uint_as_float(orow[8 * e + 1]) * inv);
-                    v.y = pack2<BF16>(__uint_as_float(orow[8 * e + 2]) * inv, __uint_as_float(orow[8 * e + 3]) * inv);
-                    v.z = pack2<BF16>(__uint_as_float(orow[8 * e + 4]) * inv, __uint_as_float(orow[8 * e + 5]) * inv);
-                    v.w = pack2<BF16>(__uint_as_float(orow[8 * e + 6]) * inv, __uint_as_float(orow[8 * e + 7]) * inv);
-                    *reinterpret_cast<uint4*>(orow_g + e * 8) = v;
-                }
-                // the group that took key tile 0 (left half) holds the reference maximum in any case
-                if (p.lse && hc == 0 && g == first_parity)
-                    p.lse[((long long)it.b * p.heads + it.h) * p.seq_q + row] = l_tot > 0.f ? m_ref * p.scale + logf(l_tot) : -INFINITY;
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&aux->l_ready));     // the epilogue warps take it from here
             t_base += it.n_kv;
         }
     }

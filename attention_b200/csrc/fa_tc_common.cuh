@@ -112,6 +112,36 @@ __device__ __forceinline__ uint64_t poly_exp2_x2(uint64_t x2) {
     return pack_u2(lo, hi);
 }
 
+// The same operations as volatile statements: the compiler keeps volatile asm statements in source order, which
+// lets a loop fix the interleaving of ex2 with the FMA-pipe work around it.
+__device__ __forceinline__ uint64_t fma2_v(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm volatile("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2_v(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm volatile("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t exp2_x2_v(uint64_t x2) {
+    uint64_t y;
+    asm volatile(
+        "{\n\t.reg .f32 lo, hi;\n\t"
+        "mov.b64 {lo, hi}, %1;\n\t"
+        "ex2.approx.ftz.f32 lo, lo;\n\t"
+        "ex2.approx.ftz.f32 hi, hi;\n\t"
+        "mov.b64 %0, {lo, hi};\n\t}"
+        : "=l"(y) : "l"(x2));
+    return y;
+}
+template <bool BF16> __device__ __forceinline__ uint32_t pack2_v(uint64_t p2) {
+    uint32_t r;
+    if (BF16) asm volatile("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.bf16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(p2));
+    else asm volatile("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.f16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(p2));
+    return r;
+}
+
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) {
     uint32_t r;
