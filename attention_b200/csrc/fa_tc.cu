@@ -82,6 +82,22 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    const int total_pairs = p.n_pairs * p.batch * p.heads;
+    // second pass: did fa_fwd_tc2_kernel flag a tile of this pair?
+    auto flagged = [&](int work) {
+        const int bh_w = work / p.n_pairs, slot_w = work % p.n_pairs;
+        const int t0 = 2 * (p.causal ? p.n_pairs - 1 - slot_w : slot_w);
+        const int slot0 = p.causal ? p.n_tiles - 1 - t0 : t0, slot1 = p.causal ? slot0 - 1 : slot0 + 1;   // fa_fwd_tc2_kernel's item order
+        return p.redo[(long long)bh_w * p.n_tiles + slot0] != 0 || (t0 + 1 < p.n_tiles && p.redo[(long long)bh_w * p.n_tiles + slot1] != 0);
+    };
+    if (p.redo) {
+        if (blockIdx.x == 0 && threadIdx.x == 0 && p.item_counter) *p.item_counter = 0;
+        // The usual case: none of this CTA's pairs is flagged.  The threads look at all of them at once and the CTA ends.
+        int any = 0;
+        for (long long c = blockIdx.x + (long long)threadIdx.x * gridDim.x; c < total_pairs; c += (long long)blockDim.x * gridDim.x) any |= flagged((int)c);
+        if (!__syncthreads_or(any)) return;
+    }
+
     if (threadIdx.x == MMA_WARP * 32) bars->abort = 0;
     if (warp == MMA_WARP) {
         __syncwarp();
@@ -92,21 +108,14 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = bars->tmem_base;
-    if (p.redo && blockIdx.x == 0 && threadIdx.x == 0 && p.item_counter) *p.item_counter = 0;
 
     // Work = one pair of query tiles of one (batch, head).  Launched on its own, every CTA has exactly one pair.  As the
     // second pass behind fa_fwd_tc2_kernel (p.redo set) the grid is one CTA per SM and a CTA walks, with the grid's
     // stride, through the pairs of which that kernel flagged a tile: normally none, and the kernel ends at once.
-    const int total_pairs = p.n_pairs * p.batch * p.heads;
     bool first_round = true;
     for (int work = blockIdx.x;; work += gridDim.x, first_round = false) {
         if (p.redo) {
-            for (; work < total_pairs; work += gridDim.x) {
-                const int bh_w = work / p.n_pairs, slot_w = work % p.n_pairs;
-                const int t0 = 2 * (p.causal ? p.n_pairs - 1 - slot_w : slot_w);
-                const int slot0 = p.causal ? p.n_tiles - 1 - t0 : t0, slot1 = p.causal ? slot0 - 1 : slot0 + 1;   // fa_fwd_tc2_kernel's item order
-                if (p.redo[(long long)bh_w * p.n_tiles + slot0] != 0 || (t0 + 1 < p.n_tiles && p.redo[(long long)bh_w * p.n_tiles + slot1] != 0)) break;
-            }
+            while (work < total_pairs && !flagged(work)) work += gridDim.x;
         }
         if (work >= total_pairs) break;
     // Consecutive work numbers are the pairs of ONE (batch, head), so the CTAs resident at any time share a few K/V
