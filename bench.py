@@ -42,10 +42,11 @@ import numpy as np  # noqa: E402
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (None until a capture exists for that kernel).
-# FA: 159 MB per launch on a quarter of C2 (profiles/fa_fwd_tc_kernel_c2small.md), scaled by the units processed.
-# Decode: read+write = 1.0057 x the algorithmic bytes (profiles/paged_decode_kernel_c3small.md).
-NCU_TRAFFIC = {"fa_fwd_tc_kernel_bytes_per_bh_pair_s4096": 158.9e6 / 32, "paged_decode_kernel_ratio": 1.0057}
+# captures summarised under profiles/ (None where no capture exists for that workload).
+# FA: 518.8 MB per launch of fa_fwd_tc2_kernel on configuration 2 in full (profiles/bench_launch_list_c2_c3.md), i.e.
+# 4.05 MB per (batch, head) pair at S=4096 D=128; scaled by the pairs a launch processes.
+# Decode: read+write = 1.0032 x the algorithmic bytes (same file).
+NCU_TRAFFIC = {"fa_fwd_tc_kernel_bytes_per_bh_pair_s4096": 518.8e6 / 128, "paged_decode_kernel_ratio": 1.0032}
 
 
 def load_peaks():
