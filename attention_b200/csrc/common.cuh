@@ -60,8 +60,8 @@ private:
     ahpc_status status_ = AHPC_SUCCESS;
 };
 
-// True when p points to memory the GPU cannot address directly (pageable or unknown host memory
-// is reported as "host"; pinned/managed/device memory as device-accessible).
+// True when p points to host memory (pageable, unknown or pinned): such tensors are staged through
+// device memory.  Device and managed memory is used in place.
 bool is_host_pointer(const void* p);
 
 // Grow-only device scratch owned by the library, one arena per (device, slot).  Used for staging

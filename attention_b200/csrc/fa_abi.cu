@@ -1,14 +1,19 @@
 // ahpc_fa_fwd: argument validation, host-pointer staging and kernel selection for the
 // FlashAttention forward.
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 
 #include "common.cuh"
 
 using namespace ahpc;
 
 namespace {
+
+constexpr int HOST_CHUNKS_MAX = 8;
 
 // Number of elements spanned by a [B,H,S,D] view with the given element strides.
 int64_t span_elems(const int64_t st[4], int64_t B, int64_t H, int64_t S, int64_t D) {
@@ -61,6 +66,84 @@ ahpc_status run(const FaLaunch& l, int requested) {
     return kernel == AHPC_FA_KERNEL_SIMT ? launch_fa_simt(l) : launch_fa_tc(l, kernel);
 }
 
+
+// ---- host tensors, dense [B,H,S,D]: copies and kernels overlapped in chunks of (batch, head) pairs ------------
+// The transfers dominate (PCIe), so the call is split into chunks whose host->device copies, kernels and
+// device->host copies run on three streams: the input copy of chunk c+1 and the output copy of chunk c-1 overlap the
+// kernel of chunk c, and the two copy directions overlap each other.
+struct HostPipe {
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t ready[HOST_CHUNKS_MAX] = {}, done[HOST_CHUNKS_MAX] = {}, start = nullptr, in_end = nullptr, out_end = nullptr;
+};
+std::mutex g_pipe_mu;
+std::map<int, HostPipe> g_pipes;
+
+ahpc_status host_pipe_for(int device, HostPipe** out) {
+    std::lock_guard<std::mutex> lock(g_pipe_mu);
+    HostPipe& hp = g_pipes[device];
+    if (!hp.in) {
+        AHPC_CUDA_OK(cudaStreamCreateWithFlags(&hp.in, cudaStreamNonBlocking));
+        AHPC_CUDA_OK(cudaStreamCreateWithFlags(&hp.out, cudaStreamNonBlocking));
+        for (int i = 0; i < HOST_CHUNKS_MAX; ++i) {
+            AHPC_CUDA_OK(cudaEventCreateWithFlags(&hp.ready[i], cudaEventDisableTiming));
+            AHPC_CUDA_OK(cudaEventCreateWithFlags(&hp.done[i], cudaEventDisableTiming));
+        }
+        AHPC_CUDA_OK(cudaEventCreateWithFlags(&hp.start, cudaEventDisableTiming));
+        AHPC_CUDA_OK(cudaEventCreateWithFlags(&hp.in_end, cudaEventDisableTiming));
+        AHPC_CUDA_OK(cudaEventCreateWithFlags(&hp.out_end, cudaEventDisableTiming));
+    }
+    *out = &hp;
+    return AHPC_SUCCESS;
+}
+
+bool dense_bhsd(const int64_t st[4], int64_t H, int64_t S, int64_t D) {
+    return st[3] == 1 && st[2] == D && st[1] == S * D && st[0] == H * S * D;
+}
+
+// All of q, k, v, out in host memory, all dense, no mask: run in chunks.  One call at a time per device uses the pipe.
+ahpc_status run_host_chunked(const ahpc_fa_args* args, FaLaunch l) {
+    static std::mutex call_mu;
+    std::lock_guard<std::mutex> call_lock(call_mu);
+    HostPipe* hp = nullptr;
+    AHPC_TRY(host_pipe_for(l.device, &hp));
+    const size_t es = dtype_size(l.dtype);
+    const int64_t pairs = (int64_t)l.batch * l.heads;
+    const int64_t q_pair = (int64_t)l.seq_q * l.head_dim, kv_pair = (int64_t)l.seq_kv * l.head_dim;
+    void *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
+    AHPC_TRY(staging_buffer(l.device, 0, pairs * q_pair * es, &dq));
+    AHPC_TRY(staging_buffer(l.device, 1, pairs * kv_pair * es, &dk));
+    AHPC_TRY(staging_buffer(l.device, 2, pairs * kv_pair * es, &dv));
+    AHPC_TRY(staging_buffer(l.device, 3, pairs * q_pair * es, &dout));
+    const int chunks = (int)std::min<int64_t>(HOST_CHUNKS_MAX, pairs);
+    // the copies may start once earlier work on the caller's stream is done (the staging arenas may still be in use there)
+    AHPC_CUDA_OK(cudaEventRecord(hp->start, l.stream));
+    AHPC_CUDA_OK(cudaStreamWaitEvent(hp->in, hp->start, 0));
+    AHPC_CUDA_OK(cudaStreamWaitEvent(hp->out, hp->start, 0));
+    for (int c = 0; c < chunks; ++c) {
+        const int64_t p0 = pairs * c / chunks, p1 = pairs * (c + 1) / chunks, n = p1 - p0;
+        auto off = [&](const void* base, int64_t per_pair) { return (char*)base + p0 * per_pair * es; };
+        AHPC_CUDA_OK(cudaMemcpyAsync(off(dq, q_pair), off(args->q, q_pair), n * q_pair * es, cudaMemcpyHostToDevice, hp->in));
+        AHPC_CUDA_OK(cudaMemcpyAsync(off(dk, kv_pair), off(args->k, kv_pair), n * kv_pair * es, cudaMemcpyHostToDevice, hp->in));
+        AHPC_CUDA_OK(cudaMemcpyAsync(off(dv, kv_pair), off(args->v, kv_pair), n * kv_pair * es, cudaMemcpyHostToDevice, hp->in));
+        AHPC_CUDA_OK(cudaEventRecord(hp->ready[c], hp->in));
+        AHPC_CUDA_OK(cudaStreamWaitEvent(l.stream, hp->ready[c], 0));
+        FaLaunch lc = l;                       // the chunk as a [1, n, S, D] tensor
+        lc.batch = 1; lc.heads = (int)n;
+        lc.q = off(dq, q_pair); lc.k = off(dk, kv_pair); lc.v = off(dv, kv_pair); lc.out = off(dout, q_pair);
+        if (l.lse) lc.lse = l.lse + p0 * l.seq_q;
+        const int64_t qs[4] = {n * q_pair, q_pair, l.head_dim, 1}, ks[4] = {n * kv_pair, kv_pair, l.head_dim, 1};
+        for (int i = 0; i < 4; ++i) { lc.qs[i] = qs[i]; lc.os[i] = qs[i]; lc.ks[i] = ks[i]; lc.vs[i] = ks[i]; }
+        AHPC_TRY(run(lc, args->kernel));
+        AHPC_CUDA_OK(cudaEventRecord(hp->done[c], l.stream));
+        AHPC_CUDA_OK(cudaStreamWaitEvent(hp->out, hp->done[c], 0));
+        AHPC_CUDA_OK(cudaMemcpyAsync(off(args->out, q_pair), off(dout, q_pair), n * q_pair * es, cudaMemcpyDeviceToHost, hp->out));
+    }
+    AHPC_CUDA_OK(cudaEventRecord(hp->out_end, hp->out));
+    AHPC_CUDA_OK(cudaStreamWaitEvent(l.stream, hp->out_end, 0));     // the caller's stream sees the whole call as done
+    AHPC_CUDA_OK(cudaStreamSynchronize(l.stream));
+    return AHPC_SUCCESS;
+}
+
 }  // namespace
 
 extern "C" {
@@ -106,6 +189,10 @@ ahpc_status ahpc_fa_fwd(const ahpc_fa_args* args) {
     // copy the result back and wait.  Spans are copied as they lie, so strided views keep working.
     if (args->lse && is_host_pointer(args->lse))
         return fail(AHPC_INVALID_INPUT, "ahpc_fa_fwd: lse must be a device pointer");
+    if (host_q && host_k && host_v && host_o && !args->mask && dense_bhsd(l.qs, l.heads, l.seq_q, l.head_dim) &&
+        dense_bhsd(l.os, l.heads, l.seq_q, l.head_dim) && dense_bhsd(l.ks, l.heads, l.seq_kv, l.head_dim) &&
+        dense_bhsd(l.vs, l.heads, l.seq_kv, l.head_dim) && (int64_t)l.batch * l.heads >= 2)
+        return run_host_chunked(args, l);
     const size_t es = dtype_size(l.dtype);
     const int64_t nq = span_elems(l.qs, l.batch, l.heads, l.seq_q, l.head_dim);
     const int64_t nk = span_elems(l.ks, l.batch, l.heads, l.seq_kv, l.head_dim);
