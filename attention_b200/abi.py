@@ -51,7 +51,7 @@ class FaArgs(C.Structure):
         ("q_strides", C.c_int64 * 4), ("k_strides", C.c_int64 * 4), ("v_strides", C.c_int64 * 4),
         ("o_strides", C.c_int64 * 4),
         ("scale", C.c_float), ("causal", C.c_int32), ("kernel", C.c_int32), ("device", C.c_int32),
-        ("stream", C.c_void_p),
+        ("stream", C.c_void_p), ("kv_heads", C.c_int32),
     ]
 
 

@@ -90,6 +90,7 @@ struct FaLaunch {                 // validated, device-pointer form of ahpc_fa_a
     const float* mask;
     float* lse;
     int dtype, batch, heads, seq_q, seq_kv, head_dim;
+    int kv_heads;                 // heads of k and v; query head h reads key/value head h / (heads / kv_heads)
     int64_t qs[4], ks[4], vs[4], os[4];
     float scale;
     int causal;

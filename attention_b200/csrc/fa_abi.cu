@@ -34,6 +34,8 @@ ahpc_status validate(const ahpc_fa_args* a) {
     if (a->kernel < AHPC_FA_KERNEL_AUTO || a->kernel > AHPC_FA_KERNEL_TC_DOUBLE_S)
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: unknown kernel selector %d", a->kernel);
     if (!std::isfinite(a->scale)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: scale is not finite");
+    if (a->kv_heads < 0 || (a->kv_heads > 0 && a->heads % a->kv_heads != 0))
+        return fail(AHPC_INVALID_PARAMETERS, "ahpc_fa_fwd: heads (%d) must be a multiple of kv_heads (%d)", a->heads, a->kv_heads);
     return AHPC_SUCCESS;
 }
 
@@ -41,6 +43,7 @@ void to_launch(const ahpc_fa_args* a, FaLaunch& l) {
     l.q = a->q; l.k = a->k; l.v = a->v; l.out = a->out; l.mask = a->mask; l.lse = a->lse;
     l.dtype = a->dtype; l.batch = a->batch; l.heads = a->heads; l.seq_q = a->seq_q; l.seq_kv = a->seq_kv;
     l.head_dim = a->head_dim;
+    l.kv_heads = a->kv_heads > 0 ? a->kv_heads : a->heads;
     for (int i = 0; i < 4; ++i) {
         l.qs[i] = a->q_strides[i]; l.ks[i] = a->k_strides[i]; l.vs[i] = a->v_strides[i]; l.os[i] = a->o_strides[i];
     }
@@ -128,7 +131,7 @@ ahpc_status run_host_chunked(const ahpc_fa_args* args, FaLaunch l) {
         AHPC_CUDA_OK(cudaEventRecord(hp->ready[c], hp->in));
         AHPC_CUDA_OK(cudaStreamWaitEvent(l.stream, hp->ready[c], 0));
         FaLaunch lc = l;                       // the chunk as a [1, n, S, D] tensor
-        lc.batch = 1; lc.heads = (int)n;
+        lc.batch = 1; lc.heads = (int)n; lc.kv_heads = (int)n;
         lc.q = off(dq, q_pair); lc.k = off(dk, kv_pair); lc.v = off(dv, kv_pair); lc.out = off(dout, q_pair);
         if (l.lse) lc.lse = l.lse + p0 * l.seq_q;
         const int64_t qs[4] = {n * q_pair, q_pair, l.head_dim, 1}, ks[4] = {n * kv_pair, kv_pair, l.head_dim, 1};
@@ -191,12 +194,12 @@ ahpc_status ahpc_fa_fwd(const ahpc_fa_args* args) {
         return fail(AHPC_INVALID_INPUT, "ahpc_fa_fwd: lse must be a device pointer");
     if (host_q && host_k && host_v && host_o && !args->mask && dense_bhsd(l.qs, l.heads, l.seq_q, l.head_dim) &&
         dense_bhsd(l.os, l.heads, l.seq_q, l.head_dim) && dense_bhsd(l.ks, l.heads, l.seq_kv, l.head_dim) &&
-        dense_bhsd(l.vs, l.heads, l.seq_kv, l.head_dim) && (int64_t)l.batch * l.heads >= 2)
+        dense_bhsd(l.vs, l.heads, l.seq_kv, l.head_dim) && l.kv_heads == l.heads && (int64_t)l.batch * l.heads >= 2)
         return run_host_chunked(args, l);
     const size_t es = dtype_size(l.dtype);
     const int64_t nq = span_elems(l.qs, l.batch, l.heads, l.seq_q, l.head_dim);
-    const int64_t nk = span_elems(l.ks, l.batch, l.heads, l.seq_kv, l.head_dim);
-    const int64_t nv = span_elems(l.vs, l.batch, l.heads, l.seq_kv, l.head_dim);
+    const int64_t nk = span_elems(l.ks, l.batch, l.kv_heads, l.seq_kv, l.head_dim);
+    const int64_t nv = span_elems(l.vs, l.batch, l.kv_heads, l.seq_kv, l.head_dim);
     const int64_t no = span_elems(l.os, l.batch, l.heads, l.seq_q, l.head_dim);
     void *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr, *dm = nullptr;
     if (host_q) { AHPC_TRY(staging_buffer(l.device, 0, nq * es, &dq)); AHPC_CUDA_OK(cudaMemcpyAsync(dq, args->q, nq * es, cudaMemcpyHostToDevice, l.stream)); l.q = dq; }

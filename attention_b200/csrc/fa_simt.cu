@@ -37,7 +37,7 @@ struct SimtParams {
     void* out;
     const float* mask;
     float* lse;
-    int batch, heads, seq_q, seq_kv, head_dim;
+    int batch, heads, seq_q, seq_kv, head_dim, kv_group;
     int64_t qs[4], ks[4], vs[4], os[4];
     float scale;
     int causal;
@@ -60,8 +60,9 @@ __global__ void __launch_bounds__(NTHREADS) fa_fwd_simt_kernel(const SimtParams 
     const int D = p.head_dim;
 
     const T* qg = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1];
-    const T* kg = static_cast<const T*>(p.k) + b * p.ks[0] + h * p.ks[1];
-    const T* vg = static_cast<const T*>(p.v) + b * p.vs[0] + h * p.vs[1];
+    const int h_kv = h / p.kv_group;                       // grouped-query attention: kv_group query heads share a key/value head
+    const T* kg = static_cast<const T*>(p.k) + b * p.ks[0] + h_kv * p.ks[1];
+    const T* vg = static_cast<const T*>(p.v) + b * p.vs[0] + h_kv * p.vs[1];
     T* og = static_cast<T*>(p.out) + b * p.os[0] + h * p.os[1];
 
     // Q tile, transposed, zero padded.
@@ -214,6 +215,7 @@ ahpc_status launch_fa_simt(const FaLaunch& a) {
     SimtParams p;
     p.q = a.q; p.k = a.k; p.v = a.v; p.out = a.out; p.mask = a.mask; p.lse = a.lse;
     p.batch = a.batch; p.heads = a.heads; p.seq_q = a.seq_q; p.seq_kv = a.seq_kv; p.head_dim = a.head_dim;
+    p.kv_group = a.heads / a.kv_heads;
     for (int i = 0; i < 4; ++i) { p.qs[i] = a.qs[i]; p.ks[i] = a.ks[i]; p.vs[i] = a.vs[i]; p.os[i] = a.os[i]; }
     p.scale = a.scale; p.causal = a.causal;
     switch (a.dtype) {

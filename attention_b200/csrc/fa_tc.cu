@@ -55,6 +55,7 @@ struct TcParams {
     float scale, scale_log2;
     int causal;
     int n_pairs;
+    int kv_group;        // query heads per key/value head
     int* error_word;
     const int* redo;     // when set: per 128-row tile flags [batch*heads][tile slot]; only flagged pairs are computed
     int n_tiles;
@@ -168,7 +169,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 mbar_expect_tx(bar, C::TILE_BYTES);
                 const CUtensorMap* map = (idx & 1) ? &map_v : &map_k;
                 for (int sub = 0; sub < C::SUBTILES; ++sub)
-                    tma_load_4d(ring_smem + slot * C::TILE_BYTES + sub * C::SUB_BYTES, map, bar, sub * 64, (idx >> 1) * BN, h, b);
+                    tma_load_4d(ring_smem + slot * C::TILE_BYTES + sub * C::SUB_BYTES, map, bar, sub * 64, (idx >> 1) * BN, h / p.kv_group, b);
                 issued = idx + 1;
             }
             if (!ok) {
@@ -518,8 +519,8 @@ ahpc_status redo_flags_for(int device, long long n, int** flags, int** counter) 
 ahpc_status launch_two_tile(const FaLaunch& a, const int* redo, int* item_counter) {
     CUtensorMap mq, mk, mv;
     AHPC_TRY(make_map(&mq, a.q, a.dtype, a.batch, a.heads, a.seq_q, a.head_dim, a.qs));
-    AHPC_TRY(make_map(&mk, a.k, a.dtype, a.batch, a.heads, a.seq_kv, a.head_dim, a.ks));
-    AHPC_TRY(make_map(&mv, a.v, a.dtype, a.batch, a.heads, a.seq_kv, a.head_dim, a.vs));
+    AHPC_TRY(make_map(&mk, a.k, a.dtype, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.ks));
+    AHPC_TRY(make_map(&mv, a.v, a.dtype, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.vs));
     TcParams p;
     p.out = a.out; p.lse = a.lse;
     p.batch = a.batch; p.heads = a.heads; p.seq_q = a.seq_q; p.seq_kv = a.seq_kv;
@@ -528,6 +529,7 @@ ahpc_status launch_two_tile(const FaLaunch& a, const int* redo, int* item_counte
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.causal = a.causal;
     p.n_pairs = (a.seq_q + 2 * BM - 1) / (2 * BM);
+    p.kv_group = a.heads / a.kv_heads;
     p.n_tiles = (a.seq_q + BM - 1) / BM;
     p.redo = redo;
     p.item_counter = item_counter;

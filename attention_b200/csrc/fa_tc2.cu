@@ -82,6 +82,7 @@ struct Tc2Params {
     int causal;
     int n_tiles;         // query tiles per (batch, head)
     int n_items;         // n_tiles * batch * heads
+    int kv_group;        // query heads per key/value head
     int* error_word;
     int* redo;           // [batch*heads][tile slot]: 1 = recompute this tile with the rescaling kernel
     int* item_counter;   // zero at launch; items beyond the first gridDim.x are drawn from it
@@ -218,7 +219,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 mbar_expect_tx(bar, C::TILE_BYTES);
                 const uint32_t dst = (is_v ? v_ring : k_ring) + slot * C::TILE_BYTES;
                 for (int sub = 0; sub < C::SUBTILES; ++sub)
-                    tma_load_4d(dst + sub * C::SUB_BYTES, is_v ? &map_v : &map_k, bar, sub * 64, j * BN, it.h, it.b);
+                    tma_load_4d(dst + sub * C::SUB_BYTES, is_v ? &map_v : &map_k, bar, sub * 64, j * BN, it.h / p.kv_group, it.b);
                 if (is_v) ++v_count; else ++k_count;
             };
             int q_loads = 0;
@@ -517,8 +518,8 @@ ahpc_status launch2(const FaLaunch& a, const CUtensorMap& mq, const CUtensorMap&
 ahpc_status launch_fa_tc2(const FaLaunch& a, int* redo_flags, int* item_counter) {
     CUtensorMap mq, mk, mv;
     AHPC_TRY(make_map(&mq, a.q, a.dtype, a.batch, a.heads, a.seq_q, a.head_dim, a.qs));
-    AHPC_TRY(make_map(&mk, a.k, a.dtype, a.batch, a.heads, a.seq_kv, a.head_dim, a.ks));
-    AHPC_TRY(make_map(&mv, a.v, a.dtype, a.batch, a.heads, a.seq_kv, a.head_dim, a.vs));
+    AHPC_TRY(make_map(&mk, a.k, a.dtype, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.ks));
+    AHPC_TRY(make_map(&mv, a.v, a.dtype, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.vs));
     Tc2Params p;
     p.out = a.out; p.lse = a.lse;
     p.batch = a.batch; p.heads = a.heads; p.seq_q = a.seq_q; p.seq_kv = a.seq_kv;
@@ -528,6 +529,7 @@ ahpc_status launch_fa_tc2(const FaLaunch& a, int* redo_flags, int* item_counter)
     p.causal = a.causal;
     p.n_tiles = (a.seq_q + BM - 1) / BM;
     p.n_items = p.n_tiles * a.batch * a.heads;
+    p.kv_group = a.heads / a.kv_heads;
     p.redo = redo_flags;
     p.item_counter = item_counter;
     AHPC_TRY(error_word_for(a.device, &p.error_word));

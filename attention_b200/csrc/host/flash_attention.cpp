@@ -22,8 +22,8 @@ void FlashAttention::configure(const AttentionParams& params, const PerformanceC
     current_perf_config_ = perf_config;
     if (params.batch_size == 0 || params.sequence_length == 0 || params.num_heads == 0 || params.head_dimension == 0)
         throw AttentionException(AttentionError::INVALID_PARAMETERS, "Invalid attention parameters: dimensions must be positive");
-    if (params.key_value_heads != 0 && params.key_value_heads != params.num_heads)
-        throw AttentionException(AttentionError::UNSUPPORTED_OPERATION, "key_value_heads != num_heads (grouped-query attention) is not supported");
+    if (params.key_value_heads != 0 && params.num_heads % params.key_value_heads != 0)
+        throw AttentionException(AttentionError::INVALID_PARAMETERS, "num_heads must be a multiple of key_value_heads");
     if (params.head_dimension > 256)
         throw AttentionException(AttentionError::UNSUPPORTED_OPERATION, "head_dimension above 256 is not supported");
     configured_elements_ = params.batch_size * params.sequence_length * params.num_heads * params.head_dimension;
@@ -54,7 +54,11 @@ void FlashAttention::forward(const TensorShape& query_shape, const void* query_d
         throw AttentionException(AttentionError::INVALID_INPUT, "Null tensor data pointer");
     const auto& qd = query_shape.dimensions;
     const auto& kd = key_shape.dimensions;
-    if (kd[0] != qd[0] || kd[2] != qd[2] || kd[3] != qd[3] || value_shape.dimensions != kd || output_shape.dimensions != qd)
+    // Grouped-query attention (AttentionParams::key_value_heads, attention_interface.hpp:61): key and value carry
+    // key_value_heads heads, query head h reads key/value head h / (num_heads / key_value_heads).
+    const size_t kv_heads = current_params_.key_value_heads != 0 ? current_params_.key_value_heads : qd[2];
+    if (kd[0] != qd[0] || (kd[2] != qd[2] && kd[2] != kv_heads) || qd[2] % kd[2] != 0 || kd[3] != qd[3] || value_shape.dimensions != kd ||
+        output_shape.dimensions != qd)
         throw AttentionException(AttentionError::INVALID_INPUT, "query/key/value/output shapes do not agree");
     if (key_shape.data_type != query_shape.data_type || value_shape.data_type != query_shape.data_type ||
         output_shape.data_type != query_shape.data_type)
@@ -67,10 +71,11 @@ void FlashAttention::forward(const TensorShape& query_shape, const void* query_d
     a.batch = static_cast<int32_t>(qd[0]); a.seq_q = static_cast<int32_t>(qd[1]);
     a.heads = static_cast<int32_t>(qd[2]); a.head_dim = static_cast<int32_t>(qd[3]);
     a.seq_kv = static_cast<int32_t>(kd[1]);
+    a.kv_heads = static_cast<int32_t>(kd[2]);
     const int layout = order_ == TensorMemoryOrder::BHSD ? AHPC_LAYOUT_BHSD : AHPC_LAYOUT_BSHD;
     ahpc_fa_strides(layout, a.batch, a.heads, a.seq_q, a.head_dim, a.q_strides);
-    ahpc_fa_strides(layout, a.batch, a.heads, a.seq_kv, a.head_dim, a.k_strides);
-    ahpc_fa_strides(layout, a.batch, a.heads, a.seq_kv, a.head_dim, a.v_strides);
+    ahpc_fa_strides(layout, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.k_strides);
+    ahpc_fa_strides(layout, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.v_strides);
     ahpc_fa_strides(layout, a.batch, a.heads, a.seq_q, a.head_dim, a.o_strides);
     // params.scale_factor and params.causal_mask are honoured (the reference's configure drops them,
     // although its tests set them: tests/test_flash_attention.cpp:108, 180).
@@ -121,7 +126,9 @@ AttentionError FlashAttention::validate_inputs(const TensorShape& q, const Tenso
                                                const AttentionParams& params) const {
     for (const TensorShape* s : {&q, &k, &v, &o}) {
         if (s->dimensions.size() != 4) return AttentionError::INVALID_INPUT;
-        if (s->dimensions[0] != params.batch_size || s->dimensions[2] != params.num_heads || s->dimensions[3] != params.head_dimension)
+        const bool kv = s == &k || s == &v;
+        const size_t heads = kv && params.key_value_heads != 0 ? params.key_value_heads : params.num_heads;
+        if (s->dimensions[0] != params.batch_size || s->dimensions[2] != heads || s->dimensions[3] != params.head_dimension)
             return AttentionError::INVALID_INPUT;
     }
     return AttentionError::SUCCESS;

@@ -38,7 +38,7 @@ def _stream_for(*tensors) -> tuple[int, int]:
 
 def flash_attention_forward(q, k, v, *, causal=False, scale=0.0, mask=None, out=None, lse=None,
                             kernel=abi.KERNEL_AUTO, device=None):
-    """out[b,h,i,:] = softmax_j(scale * q[b,h,i,:].k[b,h,j,:] + masks) . v[b,h,j,:]
+    """out[b,h,i,:] = softmax_j(scale * q[b,h,i,:].k[b,g,j,:] + masks) . v[b,g,j,:],  g = h // (H // H_kv)
 
     q, k, v: tensors indexed [B, H, S, D] (any strides: pass `x.permute(0, 2, 1, 3)` for data stored
     [B, S, H, D]).  mask: optional float32 [B, Sq, Skv], 0 = masked.  Returns `out` (allocated like q
@@ -58,6 +58,7 @@ def flash_attention_forward(q, k, v, *, causal=False, scale=0.0, mask=None, out=
         a.lse = lse.data_ptr()
     a.dtype = _dtype_code(q)
     a.batch, a.heads, a.seq_q, a.seq_kv, a.head_dim = B, H, Sq, Skv, D
+    a.kv_heads = k.shape[1]          # fewer key/value heads than query heads: grouped-query attention
     a.q_strides = (C.c_int64 * 4)(*q.stride())
     a.k_strides = (C.c_int64 * 4)(*k.stride())
     a.v_strides = (C.c_int64 * 4)(*v.stride())
@@ -79,6 +80,7 @@ def select_kernel(q, k, *, mask=None, kernel=abi.KERNEL_AUTO) -> int:
     a.dtype = _dtype_code(q)
     a.batch, a.heads, a.seq_q, a.head_dim = q.shape
     a.seq_kv = k.shape[2]
+    a.kv_heads = k.shape[1]
     a.q_strides = a.o_strides = (C.c_int64 * 4)(*q.stride())
     a.k_strides = a.v_strides = (C.c_int64 * 4)(*k.stride())
     a.kernel = kernel

@@ -112,8 +112,8 @@ AHPC_API int32_t ahpc_pointer_is_host(const void* ptr);
  * ---------------------------------------------------------------------------------------- */
 typedef struct ahpc_fa_args {
     const void* q;            /* [batch, heads, seq_q , head_dim] through q_strides  */
-    const void* k;            /* [batch, heads, seq_kv, head_dim] through k_strides  */
-    const void* v;            /* [batch, heads, seq_kv, head_dim] through v_strides  */
+    const void* k;            /* [batch, kv_heads, seq_kv, head_dim] through k_strides */
+    const void* v;            /* [batch, kv_heads, seq_kv, head_dim] through v_strides */
     void* out;                /* [batch, heads, seq_q , head_dim] through o_strides  */
     const float* mask;        /* optional float [batch, seq_q, seq_kv], 0 = masked
                                  (flash_attention.cpp:596-607); NULL = none          */
@@ -130,6 +130,9 @@ typedef struct ahpc_fa_args {
     int32_t kernel;           /* AHPC_FA_KERNEL_*                                    */
     int32_t device;           /* CUDA device ordinal                                 */
     void* stream;
+    int32_t kv_heads;         /* heads of k and v; 0 = heads.  heads must be a multiple: query head h reads
+                                 key/value head h / (heads / kv_heads) (grouped-query attention,
+                                 AttentionParams::key_value_heads, attention_interface.hpp:61) */
 } ahpc_fa_args;
 
 /* Fills strides[4] for a tensor of dims {B,S,H,D} stored in `layout`. */

@@ -51,9 +51,12 @@ def test_fa_argument_validation(native_lib):
     a.dtype = 9
     assert native_lib.ahpc_fa_fwd(C.byref(a)) == 2
     a.dtype = 0
-    a.kernel = 5
+    a.kernel = 9
     assert native_lib.ahpc_fa_fwd(C.byref(a)) == 2
     a.kernel = 0
+    a.heads, a.kv_heads = 6, 4                                            # heads is not a multiple of kv_heads
+    assert native_lib.ahpc_fa_fwd(C.byref(a)) == 2
+    a.heads, a.kv_heads = 1, 0
     a.q_strides = (C.c_int64 * 4)(-1, 0, 0, 0)
     assert native_lib.ahpc_fa_fwd(C.byref(a)) == 2
 

@@ -13,11 +13,13 @@ DEV = "cuda:0"
 
 
 def run_case(B, H, Sq, Skv, D, dtype, causal, seed, *, kernel=abi.KERNEL_AUTO, mask=None, layout="BHSD",
-             host=False, in_scale=1.0, scale=None):
+             host=False, in_scale=1.0, scale=None, kv_heads=None):
     scale = (1.0 / np.sqrt(D)) if scale is None else scale
+    Hkv = H if kv_heads is None else kv_heads
     (q,), (tq,) = u.rounded_inputs((B, H, Sq, D), dtype, seed, in_scale, 1)
-    (k, v), (tk, tv) = u.rounded_inputs((B, H, Skv, D), dtype, seed + 1, in_scale, 2)
-    want = o.attention_fwd(q, k, v, scale, causal, mask)
+    (k, v), (tk, tv) = u.rounded_inputs((B, Hkv, Skv, D), dtype, seed + 1, in_scale, 2)
+    # grouped-query attention: the oracle sees every key/value head repeated for the query heads that share it
+    want = o.attention_fwd(q, np.repeat(k, H // Hkv, axis=1), np.repeat(v, H // Hkv, axis=1), scale, causal, mask)
     if dtype != "f32":
         pass  # the oracle consumed the rounded inputs; the output is compared before rounding
     if layout == "BSHD":   # same logical values, memory stored [B,S,H,D]
@@ -143,6 +145,18 @@ def test_tc_sequence_lengths(S, causal, dtype, D, kernel):
 def test_tc_rectangular(dtype, D, kernel):
     run_case(1, 2, 300, 700, D, dtype, False, 31, kernel=kernel)
     run_case(1, 2, 700, 300, D, dtype, True, 32, kernel=kernel)
+    assert _error_word() == 0
+
+
+@pytest.mark.parametrize("kernel", [abi.KERNEL_SIMT] + TC_VARIANTS)
+@pytest.mark.parametrize("kv_heads", [1, 2, 4])
+def test_grouped_query_attention(kernel, kv_heads):
+    """AttentionParams::key_value_heads (attention_interface.hpp:61): 8 query heads over 1, 2 or 4 key/value heads."""
+    run_case(2, 8, 300, 300, 128, "bf16", True, 61 + kv_heads, kernel=kernel, kv_heads=kv_heads)
+    run_case(1, 8, 200, 333, 64, "f16", False, 71 + kv_heads, kernel=kernel, kv_heads=kv_heads)
+    if kernel == abi.KERNEL_SIMT:
+        run_case(1, 8, 65, 65, 32, "f32", True, 81 + kv_heads, kernel=kernel, kv_heads=kv_heads)
+        run_case(1, 8, 16, 16, 64, "f32", False, 91 + kv_heads, kernel=kernel, kv_heads=kv_heads, host=True)
     assert _error_word() == 0
 
 
