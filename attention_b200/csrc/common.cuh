@@ -100,6 +100,7 @@ struct FaLaunch {                 // validated, device-pointer form of ahpc_fa_a
 ahpc_status launch_fa_simt(const FaLaunch& a);     // fa_simt.cu
 ahpc_status launch_fa_tc(const FaLaunch& a, int variant);        // fa_tc.cu; variant = AHPC_FA_KERNEL_TC (library's choice), _TC_TWO_TILE or _TC_DOUBLE_S
 ahpc_status launch_fa_tc2(const FaLaunch& a, int* redo_flags, int* item_counter);   // fa_tc2.cu
+int fa_tc2_bh_group(const FaLaunch& a);                                              // fa_tc2.cu: group size of its item order
 bool fa_tc_supported(const FaLaunch& a, const char** why);
 ahpc_status fa_tc_read_error_word(int device, int* out);   // fa_tc.cu
 

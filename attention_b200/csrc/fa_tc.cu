@@ -59,6 +59,7 @@ struct TcParams {
     int* error_word;
     const int* redo;     // when set: per 128-row tile flags [batch*heads][tile slot]; only flagged pairs are computed
     int n_tiles;
+    int bh_group;        // group size of fa_fwd_tc2_kernel's item order (ItemOrder), for the flag lookup
     int* item_counter;   // when set: the item counter of the preceding fa_fwd_tc2_kernel launch, put back to zero here
 };
 
@@ -89,7 +90,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int bh_w = work / p.n_pairs, slot_w = work % p.n_pairs;
         const int t0 = 2 * (p.causal ? p.n_pairs - 1 - slot_w : slot_w);
         const int slot0 = p.causal ? p.n_tiles - 1 - t0 : t0, slot1 = p.causal ? slot0 - 1 : slot0 + 1;   // fa_fwd_tc2_kernel's item order
-        return p.redo[(long long)bh_w * p.n_tiles + slot0] != 0 || (t0 + 1 < p.n_tiles && p.redo[(long long)bh_w * p.n_tiles + slot1] != 0);
+        const ItemOrder order{p.n_tiles, p.batch * p.heads, p.bh_group};
+        return p.redo[order.encode(bh_w, slot0)] != 0 || (t0 + 1 < p.n_tiles && p.redo[order.encode(bh_w, slot1)] != 0);
     };
     if (p.redo) {
         if (blockIdx.x == 0 && threadIdx.x == 0 && p.item_counter) *p.item_counter = 0;
@@ -533,6 +535,7 @@ ahpc_status launch_two_tile(const FaLaunch& a, const int* redo, int* item_counte
     p.n_tiles = (a.seq_q + BM - 1) / BM;
     p.redo = redo;
     p.item_counter = item_counter;
+    p.bh_group = redo ? fa_tc2_bh_group(a) : 1;
     AHPC_TRY(error_word_for(a.device, &p.error_word));
     const bool bf16 = a.dtype == AHPC_BF16;
     if (a.head_dim == 128) return bf16 ? launch<128, true>(a, mq, mk, mv, p) : launch<128, false>(a, mq, mk, mv, p);

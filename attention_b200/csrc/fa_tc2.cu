@@ -17,7 +17,7 @@
 //   warp  17    lane 0 issues the tcgen05.mma of O += P V (two issuing threads: the waits and commits of
 //               one overlap the MMAs of the other, so the tensor pipe is not idle while a thread waits)
 //   warp  18    lane 0 issues the TMA loads (Q per item, K and V tiles through two rings)
-//   warp  19    lane 0 draws the next items from the global counter, two ahead of the other roles
+//   warp  19    lane 0 draws the next item from the global counter, one ahead of the slowest role
 //   warps 20-23 epilogue: O / row sum -> global memory, while the softmax warps are already on the next item
 //
 // Because P has its own columns, a score buffer is free again as soon as its softmax warps have
@@ -60,14 +60,19 @@ constexpr int SOFTMAX_REGS = 96, OTHER_REGS = 48;
 #define AHPC_TC2_POLY 0x0
 #endif
 constexpr uint32_t POLY_PATTERN = AHPC_TC2_POLY;
+#ifndef AHPC_TC2_SCALAR
+#define AHPC_TC2_SCALAR 0
+#endif
 
 template <int D> struct Cfg2 {
     static constexpr int SUBTILES = D / 64;                  // 64-element (128-byte) wide column blocks
     static constexpr uint32_t TILE_BYTES = BN * D * 2;        // one Q, K or V tile
     static constexpr uint32_t SUB_BYTES = BN * 128;           // one 128-row x 128-byte swizzled block
-    static constexpr int RING = D == 128 ? 3 : 6;             // depth of the K ring and of the V ring (tiles each)
-    static constexpr int LEAD = 4;                            // K tiles are requested this many key tiles ahead of V tiles
-    static constexpr uint32_t SMEM_TILES = (1 + 2 * RING) * TILE_BYTES;
+    // Two Q buffers (the next item's Q arrives while this item runs), a K ring and a V ring.  K tiles are consumed
+    // early (S runs ahead of the softmax) and released early, V tiles late: the K ring may be the shallower one.
+    static constexpr int K_RING = D == 128 ? 2 : 6, V_RING = D == 128 ? 3 : 6;
+    static constexpr int LEAD = 2;                            // K tiles are requested this many key tiles ahead of V tiles
+    static constexpr uint32_t SMEM_TILES = (2 + K_RING + V_RING) * TILE_BYTES;
     static constexpr uint32_t AUX_BYTES = 3072;               // barriers + per-row exchange arrays
     static constexpr uint32_t SMEM_BYTES = SMEM_TILES + AUX_BYTES;   // 232448 for head_dim 128: all of an SM's shared memory
     static constexpr uint32_t P_COL = 256, O_COL = 384;
@@ -83,13 +88,23 @@ struct Tc2Params {
     int n_tiles;         // query tiles per (batch, head)
     int n_items;         // n_tiles * batch * heads
     int kv_group;        // query heads per key/value head
+    int bh_group;        // (batch, head) pairs per group of the item order (ItemOrder)
     int* error_word;
     int* redo;           // [batch*heads][tile slot]: 1 = recompute this tile with the rescaling kernel
     int* item_counter;   // zero at launch; items beyond the first gridDim.x are drawn from it
 };
 
+#ifdef AHPC_TC2_STATS
+__device__ long long g_tc2_stats[256 * 8];      // experiment builds: per CTA {cycles, items, tiles, wait s_full, wait p_free, wait m_ready, wait item}
+#define STAT_T0() const long long st_t0_ = clock64()
+#define STAT_ADD(x) (x) += clock64() - st_t0_
+#else
+#define STAT_T0()
+#define STAT_ADD(x)
+#endif
+
 struct Aux2 {            // lives behind the tiles in shared memory
-    uint64_t q_full, q_free, s_full[2], s_free[2], p_full[2], p_free[2], o_done, o_free;
+    uint64_t q_full[2], q_free[2], s_full[2], s_free[2], p_full[2], p_free[2], o_done, o_free;
     uint64_t m_ready, m_taken, l_ready, l_taken, item_full[2], item_empty[2];
     uint64_t k_full[6], k_empty[6], v_full[6], v_empty[6];
     uint32_t tmem_base;
@@ -113,18 +128,18 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     constexpr float GROW_SUM_LIMIT = BF16 ? 1.8446744e19f : 32768.0f;
     extern __shared__ __align__(1024) uint8_t smem_raw[];     // 128-byte-swizzled tiles need 1024-byte alignment
     const uint32_t smem_base = smem_u32(smem_raw);
-    const uint32_t q_smem = smem_base;
-    const uint32_t k_ring = smem_base + C::TILE_BYTES;
-    const uint32_t v_ring = k_ring + C::RING * C::TILE_BYTES;
+    const uint32_t q_smem = smem_base;                                   // two buffers: item k uses buffer k & 1
+    const uint32_t k_ring = smem_base + 2 * C::TILE_BYTES;
+    const uint32_t v_ring = k_ring + C::K_RING * C::TILE_BYTES;
     Aux2* aux = reinterpret_cast<Aux2*>(smem_raw + C::SMEM_TILES);
     volatile int* abort_flag = &aux->abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == S_WARP * 32) {
-        mbar_init(smem_u32(&aux->q_full), 1);
-        mbar_init(smem_u32(&aux->q_free), 1);
         for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&aux->q_full[i]), 1);
+            mbar_init(smem_u32(&aux->q_free[i]), 1);
             mbar_init(smem_u32(&aux->s_full[i]), 1);
             mbar_init(smem_u32(&aux->s_free[i]), 8);
             mbar_init(smem_u32(&aux->p_full[i]), 8);
@@ -138,9 +153,11 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         mbar_init(smem_u32(&aux->m_taken), SOFTMAX_WARPS);
         mbar_init(smem_u32(&aux->l_ready), SOFTMAX_WARPS);
         mbar_init(smem_u32(&aux->l_taken), 4);
-        for (int s = 0; s < C::RING; ++s) {
+        for (int s = 0; s < C::K_RING; ++s) {
             mbar_init(smem_u32(&aux->k_full[s]), 1);
             mbar_init(smem_u32(&aux->k_empty[s]), 1);
+        }
+        for (int s = 0; s < C::V_RING; ++s) {
             mbar_init(smem_u32(&aux->v_full[s]), 1);
             mbar_init(smem_u32(&aux->v_empty[s]), 1);
         }
@@ -158,13 +175,14 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem = aux->tmem_base;
 
-    // Item number -> (batch, head, first query row, key tiles).  Consecutive items are the query tiles of ONE
-    // (batch, head), so the CTAs resident at any time share a few K/V streams and those stay in L2; heavy (late)
-    // tiles first when causal.
+    // Item number -> (batch, head, first query row, key tiles), in the order of ItemOrder: few (batch, head) pairs at a
+    // time, so that the CTAs resident at any time share a few K/V streams and those stay in L2; heavy (late) tiles
+    // first when causal.
     struct Item { int b, h, q0, n_kv; };
     auto decode = [&](int w) {
         Item it;
-        const int bh = w / p.n_tiles, slot = w % p.n_tiles;
+        int bh, slot;
+        ItemOrder{p.n_tiles, p.batch * p.heads, p.bh_group}.decode(w, bh, slot);
         const int tile = p.causal ? p.n_tiles - 1 - slot : slot;
         it.b = bh / p.heads;
         it.h = bh % p.heads;
@@ -190,7 +208,9 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         // ------------------------------------------------------------------ item scheduler
         if (lane == 0) {
             for (int k = 0;; ++k) {
-                if (k >= 2 && !wait_bounded(smem_u32(&aux->item_empty[k & 1]), ((k - 2) >> 1) & 1, abort_flag, p.error_word, 1400)) break;
+                // One item ahead: item k is drawn once every role has taken item k-1 (drawing further ahead leaves a CTA
+                // with a queue of its own when the counter runs out, while others are already idle).
+                if (k >= 1 && !wait_bounded(smem_u32(&aux->item_empty[(k - 1) & 1]), ((k - 1) >> 1) & 1, abort_flag, p.error_word, 1400)) break;
                 int w = k == 0 ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.item_counter, 1);
                 if (w >= p.n_items) w = -1;
                 aux->item[k & 1] = w;
@@ -209,8 +229,8 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             int k_count = 0, v_count = 0;          // K / V tiles requested so far, over all items
             Item it{};
             auto load_tile = [&](bool is_v, int j) {
-                const int cnt = is_v ? v_count : k_count;
-                const int slot = cnt % C::RING, round = cnt / C::RING;
+                const int cnt = is_v ? v_count : k_count, ring = is_v ? C::V_RING : C::K_RING;
+                const int slot = cnt % ring, round = cnt / ring;
                 uint64_t* full = is_v ? aux->v_full : aux->k_full;
                 uint64_t* empty = is_v ? aux->v_empty : aux->k_empty;
                 if (round > 0) ok = wait_bounded(smem_u32(&empty[slot]), (round - 1) & 1, abort_flag, p.error_word, (is_v ? 1110 : 1100) + slot);
@@ -227,14 +247,14 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const int w = next_item(k, 1410, false);
                 if (w < 0) break;
                 it = decode(w);
-                // Q's buffer is free when the last S MMA of the previous item has completed
-                if (k > 0) ok = wait_bounded(smem_u32(&aux->q_free), (k - 1) & 1, abort_flag, p.error_word, 1120);
+                // Q buffer k & 1 is free when the last S MMA of item k-2 has completed
+                if (k >= 2) ok = wait_bounded(smem_u32(&aux->q_free[k & 1]), ((k - 2) >> 1) & 1, abort_flag, p.error_word, 1120);
                 if (!ok) break;
                 {
-                    const uint32_t bar = smem_u32(&aux->q_full);
+                    const uint32_t bar = smem_u32(&aux->q_full[k & 1]);
                     mbar_expect_tx(bar, C::TILE_BYTES);
                     for (int sub = 0; sub < C::SUBTILES; ++sub)
-                        tma_load_4d(q_smem + sub * C::SUB_BYTES, &map_q, bar, sub * 64, it.q0, it.h, it.b);
+                        tma_load_4d(q_smem + (k & 1) * C::TILE_BYTES + sub * C::SUB_BYTES, &map_q, bar, sub * 64, it.q0, it.h, it.b);
                     ++q_loads;
                 }
                 // K tiles run LEAD key tiles ahead of V tiles: S = Q K^T is computed ahead of the softmax, O += P V behind it.
@@ -246,17 +266,17 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
             if (!ok) {
                 // Leave no copy in flight: wait (bounded) for the loads of the last ring round requested and for Q.
-                for (int c = max(0, k_count - C::RING); c < k_count; ++c) {
+                for (int c = max(0, k_count - C::K_RING); c < k_count; ++c) {
                     long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&aux->k_full[c % C::RING]), (c / C::RING) & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
+                    while (!mbar_try_wait(smem_u32(&aux->k_full[c % C::K_RING]), (c / C::K_RING) & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
                 }
-                for (int c = max(0, v_count - C::RING); c < v_count; ++c) {
+                for (int c = max(0, v_count - C::V_RING); c < v_count; ++c) {
                     long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&aux->v_full[c % C::RING]), (c / C::RING) & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
+                    while (!mbar_try_wait(smem_u32(&aux->v_full[c % C::V_RING]), (c / C::V_RING) & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
                 }
-                if (q_loads > 0) {
+                for (int c = max(0, q_loads - 2); c < q_loads; ++c) {
                     long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&aux->q_full), (q_loads - 1) & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
+                    while (!mbar_try_wait(smem_u32(&aux->q_full[c & 1]), (c >> 1) & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
                 }
             }
         }
@@ -265,19 +285,19 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         // ------------------------------------------------------------------ issuer of S = Q K^T
         if (lane == 0) {
             constexpr uint32_t IDESC_S = idesc_f16(BF16 ? 1 : 0, BM, BN, 0, 0);     // Q (K-major) x K (K-major)
-            const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
             bool ok = true;
             int t = 0;                                  // key tiles issued so far, over all items
             for (int k = 0; ok; ++k) {
                 const int w = next_item(k, 1420, false);
                 if (w < 0) break;
                 const Item it = decode(w);
-                ok = wait_bounded(smem_u32(&aux->q_full), k & 1, abort_flag, p.error_word, 1200);
+                ok = wait_bounded(smem_u32(&aux->q_full[k & 1]), (k >> 1) & 1, abort_flag, p.error_word, 1200);
+                const uint64_t q_desc = smem_desc_sw128(q_smem + (k & 1) * C::TILE_BYTES, 16, 1024);
                 // S[t & 1] = Q K_j^T : head_dim/16 MMAs of K = 16.  Needs K_j in shared memory and, from the third tile on,
                 // the softmax warps of the tile two back to have copied that buffer out.
                 for (int j = 0; j < it.n_kv && ok; ++j, ++t) {
-                    const int slot = t % C::RING, buf = t & 1;
-                    ok = wait_bounded(smem_u32(&aux->k_full[slot]), (t / C::RING) & 1, abort_flag, p.error_word, 1220);
+                    const int slot = t % C::K_RING, buf = t & 1;
+                    ok = wait_bounded(smem_u32(&aux->k_full[slot]), (t / C::K_RING) & 1, abort_flag, p.error_word, 1220);
                     if (ok && t >= 2) ok = wait_bounded(smem_u32(&aux->s_free[buf]), ((t - 2) >> 1) & 1, abort_flag, p.error_word, 1230 + buf);
                     if (!ok) break;
                     tc_fence_after_sync();
@@ -290,7 +310,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     tc_commit(smem_u32(&aux->s_full[buf]));
                     tc_commit(smem_u32(&aux->k_empty[slot]));
                 }
-                if (ok) tc_commit(smem_u32(&aux->q_free));
+                if (ok) tc_commit(smem_u32(&aux->q_free[k & 1]));
             }
         }
     } else if (warp == O_WARP) {
@@ -306,8 +326,8 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const Item it = decode(w);
                 // O (+)= P[t & 1] V_j : 8 MMAs of K = 16 keys; V is MN-major (head_dim contiguous)
                 for (int j = 0; j < it.n_kv && ok; ++j, ++t) {
-                    const int slot = t % C::RING, buf = t & 1;
-                    ok = wait_bounded(smem_u32(&aux->v_full[slot]), (t / C::RING) & 1, abort_flag, p.error_word, 1240);
+                    const int slot = t % C::V_RING, buf = t & 1;
+                    ok = wait_bounded(smem_u32(&aux->v_full[slot]), (t / C::V_RING) & 1, abort_flag, p.error_word, 1240);
                     if (ok) ok = wait_bounded(smem_u32(&aux->p_full[buf]), (t >> 1) & 1, abort_flag, p.error_word, 1250 + buf);
                     // the first MMA of an item overwrites O: the previous item's epilogue must have copied it out
                     if (ok && j == 0 && k > 0) ok = wait_bounded(smem_u32(&aux->o_free), (k - 1) & 1, abort_flag, p.error_word, 1260);
@@ -384,9 +404,14 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         bool ok = true;
         int t_base = 0;          // key tiles of all earlier items
         int mine = 0;            // key tiles this warp has processed, over all items
+#ifdef AHPC_TC2_STATS
+        const long long st_start = clock64();
+        long long st_items = 0, st_tiles = 0, st_s = 0, st_p = 0, st_m = 0, st_i = 0;
+#endif
 
         for (int k = 0; ok; ++k) {
-            const int w = next_item(k, 1440, true);
+            int w;
+            { STAT_T0(); w = next_item(k, 1440, true); STAT_ADD(st_i); }
             if (w < 0) break;
             const Item it = decode(w);
             const int row = it.q0 + r_in_tile;
@@ -396,7 +421,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (warp == 0 && lane == 0) p.redo[w] = 0;            // a row that outgrows the reference sets it below
 
             for (int j = g ^ first_parity; j < it.n_kv; j += 2, ++mine) {
-                ok = wait_bounded(smem_u32(&aux->s_full[g]), mine & 1, abort_flag, p.error_word, 1300 + g);
+                { STAT_T0(); ok = wait_bounded(smem_u32(&aux->s_full[g]), mine & 1, abort_flag, p.error_word, 1300 + g); STAT_ADD(st_s); }
                 if (!ok) break;
                 tc_fence_after_sync();
                 const int k0 = j * BN + hc * 64;                                            // first key of this warp's columns
@@ -434,7 +459,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     if (lane == 0) mbar_arrive(smem_u32(&aux->m_ready));
                 }
                 if (!have_m) {
-                    ok = wait_bounded(smem_u32(&aux->m_ready), k & 1, abort_flag, p.error_word, 1320);
+                    { STAT_T0(); ok = wait_bounded(smem_u32(&aux->m_ready), k & 1, abort_flag, p.error_word, 1320); STAT_ADD(st_m); }
                     if (!ok) break;
                     m_ref = fmaxf(aux->l_part[0][r_in_tile], aux->l_part[1][r_in_tile]);
                     if (hc == 0 && g == first_parity) aux->m_ref[r_in_tile] = m_ref;      // for the epilogue warps (log-sum-exp)
@@ -442,18 +467,24 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     if (lane == 0) mbar_arrive(smem_u32(&aux->m_taken));
                     have_m = true;
                 }
-                if (mine >= 1) {       // P[g] may still feed the PV MMA of this parity's previous tile (normally long done)
-                    ok = wait_bounded(smem_u32(&aux->p_free[g]), (mine - 1) & 1, abort_flag, p.error_word, 1330 + g);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                }
                 const uint64_t negm2 = pack_f2(-m_ref * p.scale_log2, -m_ref * p.scale_log2);
                 uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};                                // four packed partial row sums
+#if AHPC_TC2_SCALAR
+                float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                const float negm_s = -m_ref * p.scale_log2;
+                (void)sum2; (void)negm2;
+#endif
+                uint32_t packed[2][16];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    uint32_t packed[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
+#if AHPC_TC2_SCALAR
+                        const float x0 = fmaf(__uint_as_float(sr[c][2 * e]), p.scale_log2, negm_s), x1 = fmaf(__uint_as_float(sr[c][2 * e + 1]), p.scale_log2, negm_s);
+                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                        sums[e & 3] += p0; sums[4 + (e & 3)] += p1;
+                        packed[c][e] = pack2<BF16>(p0, p1);
+#else
                         const uint64_t x2 = fma2(pack_u2(sr[c][2 * e], sr[c][2 * e + 1]), scale2, negm2);
                         uint64_t p2;
                         if ((POLY_PATTERN >> (e & 7)) & 1u) {
@@ -462,12 +493,25 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                             p2 = pack_f2(fast_exp2(__uint_as_float((uint32_t)x2)), fast_exp2(__uint_as_float((uint32_t)(x2 >> 32))));
                         }
                         sum2[e & 3] = add2(sum2[e & 3], p2);
-                        packed[e] = pack2<BF16>(__uint_as_float((uint32_t)p2), __uint_as_float((uint32_t)(p2 >> 32)));
+                        packed[c][e] = pack2<BF16>(__uint_as_float((uint32_t)p2), __uint_as_float((uint32_t)(p2 >> 32)));
+#endif
                     }
-                    tmem_st16(p_addr + c * 16, packed);
                 }
+                // P[g] still feeds the PV MMA of this parity's previous tile for a while after that tile's softmax ended:
+                // the probabilities wait in registers, the store comes last.
+                if (mine >= 1) {
+                    { STAT_T0(); ok = wait_bounded(smem_u32(&aux->p_free[g]), (mine - 1) & 1, abort_flag, p.error_word, 1330 + g); STAT_ADD(st_p); }
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
+                tmem_st16(p_addr, packed[0]);
+                tmem_st16(p_addr + 16, packed[1]);
+#if AHPC_TC2_SCALAR
+                const float psum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
+#else
                 const uint64_t tot = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
                 const float psum = __uint_as_float((uint32_t)tot) + __uint_as_float((uint32_t)(tot >> 32));
+#endif
                 // A probability beyond the range reserved for P means the reference maximum is too stale for this row.
                 grew |= !(psum < GROW_SUM_LIMIT);
                 l_run += psum;
@@ -491,7 +535,16 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&aux->l_ready));     // the epilogue warps take it from here
             t_base += it.n_kv;
+#ifdef AHPC_TC2_STATS
+            ++st_items; st_tiles += it.n_kv;
+#endif
         }
+#ifdef AHPC_TC2_STATS
+        if (warp == 0 && lane == 0 && blockIdx.x < 256) {
+            long long* o = g_tc2_stats + blockIdx.x * 8;
+            o[0] = clock64() - st_start; o[1] = st_items; o[2] = st_tiles; o[3] = st_s; o[4] = st_p; o[5] = st_m; o[6] = st_i;
+        }
+#endif
     }
 
     tc_fence_before_sync();
@@ -515,6 +568,15 @@ ahpc_status launch2(const FaLaunch& a, const CUtensorMap& mq, const CUtensorMap&
 
 }  // namespace
 
+// (batch, head) pairs per group of the item order: causal work is uneven, so a group holds about two items per SM and
+// its heavy tiles go out first; otherwise one pair at a time (all items weigh the same, fewest K/V streams live).
+int fa_tc2_bh_group(const FaLaunch& a) {
+    if (!a.causal) return 1;
+    const int n_tiles = (a.seq_q + BM - 1) / BM;
+    const int want = (2 * std::max(1, sm_count(a.device)) + n_tiles - 1) / n_tiles;
+    return std::max(1, std::min(want, a.batch * a.heads));
+}
+
 ahpc_status launch_fa_tc2(const FaLaunch& a, int* redo_flags, int* item_counter) {
     CUtensorMap mq, mk, mv;
     AHPC_TRY(make_map(&mq, a.q, a.dtype, a.batch, a.heads, a.seq_q, a.head_dim, a.qs));
@@ -530,6 +592,7 @@ ahpc_status launch_fa_tc2(const FaLaunch& a, int* redo_flags, int* item_counter)
     p.n_tiles = (a.seq_q + BM - 1) / BM;
     p.n_items = p.n_tiles * a.batch * a.heads;
     p.kv_group = a.heads / a.kv_heads;
+    p.bh_group = fa_tc2_bh_group(a);
     p.redo = redo_flags;
     p.item_counter = item_counter;
     AHPC_TRY(error_word_for(a.device, &p.error_word));
@@ -539,3 +602,10 @@ ahpc_status launch_fa_tc2(const FaLaunch& a, int* redo_flags, int* item_counter)
 }
 
 }  // namespace ahpc
+
+#ifdef AHPC_TC2_STATS
+extern "C" __attribute__((visibility("default"))) void ahpc_tc2_stats_read(long long* out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, ahpc::g_tc2_stats, sizeof(long long) * 256 * 8);
+}
+#endif

@@ -155,6 +155,26 @@ template <> __device__ __forceinline__ uint32_t pack2<false>(float lo, float hi)
 }
 
 
+// Order in which fa_fwd_tc2_kernel's CTAs draw their items (query tile, batch*head): the (batch, head) pairs are
+// taken in groups of `group`; inside a group all pairs' tiles of slot 0 come first, then slot 1, ...  (slot 0 is the
+// heaviest tile when causal).  A group keeps few K/V streams live at a time (they stay in L2); slot-major order inside
+// it hands the heavy tiles out first, so that the light ones fill the end and the CTAs finish together.
+struct ItemOrder {
+    int n_tiles, bh_count, group;
+    __host__ __device__ void decode(int w, int& bh, int& slot) const {
+        const int per_group = group * n_tiles;
+        const int gi = w / per_group, r = w - gi * per_group;
+        const int members = min(group, bh_count - gi * group);
+        slot = r / members;
+        bh = gi * group + (r - slot * members);
+    }
+    __host__ __device__ int encode(int bh, int slot) const {
+        const int gi = bh / group;
+        const int members = min(group, bh_count - gi * group);
+        return gi * group * n_tiles + slot * members + (bh - gi * group);
+    }
+};
+
 // ---- host helpers (defined in fa_tc.cu) ----------------------------------------------------------
 // 4-d tensor map (dim, position, head, batch) over a [B,H,S,D] view with element strides st; the box
 // is 64 elements (128 bytes, swizzled) by `box_rows` positions.
