@@ -60,9 +60,6 @@ constexpr int SOFTMAX_REGS = 96, OTHER_REGS = 48;
 #define AHPC_TC2_POLY 0x0
 #endif
 constexpr uint32_t POLY_PATTERN = AHPC_TC2_POLY;
-#ifndef AHPC_TC2_SCALAR
-#define AHPC_TC2_SCALAR 0
-#endif
 
 template <int D> struct Cfg2 {
     static constexpr int SUBTILES = D / 64;                  // 64-element (128-byte) wide column blocks
@@ -469,22 +466,11 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 const uint64_t negm2 = pack_f2(-m_ref * p.scale_log2, -m_ref * p.scale_log2);
                 uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};                                // four packed partial row sums
-#if AHPC_TC2_SCALAR
-                float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                const float negm_s = -m_ref * p.scale_log2;
-                (void)sum2; (void)negm2;
-#endif
                 uint32_t packed[2][16];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
-#if AHPC_TC2_SCALAR
-                        const float x0 = fmaf(__uint_as_float(sr[c][2 * e]), p.scale_log2, negm_s), x1 = fmaf(__uint_as_float(sr[c][2 * e + 1]), p.scale_log2, negm_s);
-                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                        sums[e & 3] += p0; sums[4 + (e & 3)] += p1;
-                        packed[c][e] = pack2<BF16>(p0, p1);
-#else
                         const uint64_t x2 = fma2(pack_u2(sr[c][2 * e], sr[c][2 * e + 1]), scale2, negm2);
                         uint64_t p2;
                         if ((POLY_PATTERN >> (e & 7)) & 1u) {
@@ -494,7 +480,6 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         }
                         sum2[e & 3] = add2(sum2[e & 3], p2);
                         packed[c][e] = pack2<BF16>(__uint_as_float((uint32_t)p2), __uint_as_float((uint32_t)(p2 >> 32)));
-#endif
                     }
                 }
                 // P[g] still feeds the PV MMA of this parity's previous tile for a while after that tile's softmax ended:
@@ -506,12 +491,8 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 tmem_st16(p_addr, packed[0]);
                 tmem_st16(p_addr + 16, packed[1]);
-#if AHPC_TC2_SCALAR
-                const float psum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
-#else
                 const uint64_t tot = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
                 const float psum = __uint_as_float((uint32_t)tot) + __uint_as_float((uint32_t)(tot >> 32));
-#endif
                 // A probability beyond the range reserved for P means the reference maximum is too stale for this row.
                 grew |= !(psum < GROW_SUM_LIMIT);
                 l_run += psum;
