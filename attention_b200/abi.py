@@ -67,7 +67,7 @@ class DecodeArgs(C.Structure):
     _fields_ = [
         ("pool", C.c_void_p), ("seqs", C.POINTER(C.c_int32)), ("n_seqs", C.c_int32),
         ("q", C.c_void_p), ("out", C.c_void_p), ("qo_dtype", C.c_int32), ("scale", C.c_float),
-        ("split_tokens", C.c_int32), ("stream", C.c_void_p),
+        ("split_tokens", C.c_int32), ("stream", C.c_void_p), ("q_heads", C.c_int32),
     ]
 
 

@@ -30,7 +30,7 @@ void PagedAttention::create_pool() {
     destroy_pool();
     const AttentionParams& p = current_params_;
     const size_t page_tokens = paged_config_.page_size ? paged_config_.page_size : p.page_size;
-    const size_t page_bytes = 2 * page_tokens * p.num_heads * p.head_dimension * dtype_bytes(paged_config_.kv_cache_dtype);
+    const size_t page_bytes = 2 * page_tokens * (p.key_value_heads != 0 ? p.key_value_heads : p.num_heads) * p.head_dimension * dtype_bytes(paged_config_.kv_cache_dtype);
     size_t pages = std::max(paged_config_.initial_page_pool_size, paged_config_.memory_pool_size / std::max<size_t>(1, page_bytes));
     pages = std::min<size_t>(std::max<size_t>(pages, 1), 0x7fffffff);
     ahpc_pool_config cfg{};
@@ -38,7 +38,7 @@ void PagedAttention::create_pool() {
     cfg.dtype = static_cast<int32_t>(paged_config_.kv_cache_dtype);
     cfg.num_pages = static_cast<int32_t>(pages);
     cfg.page_size = static_cast<int32_t>(page_tokens);
-    cfg.heads = static_cast<int32_t>(p.num_heads);
+    cfg.heads = static_cast<int32_t>(p.key_value_heads != 0 ? p.key_value_heads : p.num_heads);
     cfg.head_dim = static_cast<int32_t>(p.head_dimension);
     cfg.max_seqs = static_cast<int32_t>(std::max<size_t>(1, paged_config_.max_concurrent_sequences));
     cfg.max_pages_per_seq = static_cast<int32_t>(std::max<size_t>(1, paged_config_.max_pages_per_sequence));
@@ -51,8 +51,10 @@ void PagedAttention::configure(const AttentionParams& params, const PerformanceC
     current_perf_config_ = perf_config;
     if (params.batch_size == 0 || params.sequence_length == 0 || params.num_heads == 0 || params.head_dimension == 0)
         throw AttentionException(AttentionError::INVALID_PARAMETERS, "Invalid attention parameters: dimensions must be positive");
-    if (params.key_value_heads != 0 && params.key_value_heads != params.num_heads)
-        throw AttentionException(AttentionError::UNSUPPORTED_OPERATION, "key_value_heads != num_heads (grouped-query attention) is not supported");
+    // Grouped-query attention (AttentionParams::key_value_heads, attention_interface.hpp:61): the pool holds
+    // key_value_heads heads, queries carry num_heads; query head h reads key/value head h / (num_heads / key_value_heads).
+    if (params.key_value_heads != 0 && params.num_heads % params.key_value_heads != 0)
+        throw AttentionException(AttentionError::INVALID_PARAMETERS, "num_heads must be a multiple of key_value_heads");
     if (params.page_size != 0 && paged_config_.page_size == PagedAttentionConfig{}.page_size) paged_config_.page_size = params.page_size;
     std::lock_guard<std::mutex> lock(sequences_mutex_);
     create_pool();
@@ -78,7 +80,7 @@ void PagedAttention::forward(const TensorShape& query_shape, const void* query_d
         throw AttentionException(AttentionError::INVALID_INPUT, "Null tensor data pointer");
     const auto& qd = query_shape.dimensions;
     const auto& kd = key_shape.dimensions;
-    if (kd[0] != qd[0] || kd[2] != qd[2] || kd[3] != qd[3] || value_shape.dimensions != kd || output_shape.dimensions != qd)
+    if (kd[0] != qd[0] || kd[2] == 0 || qd[2] % kd[2] != 0 || kd[3] != qd[3] || value_shape.dimensions != kd || output_shape.dimensions != qd)
         throw AttentionException(AttentionError::INVALID_INPUT, "query/key/value/output shapes do not agree");
     // All query tokens against the whole K/V: the result the temporary-sequence path of the reference
     // means to produce, computed by the dense forward kernel without a detour through pages.
@@ -89,9 +91,10 @@ void PagedAttention::forward(const TensorShape& query_shape, const void* query_d
     a.batch = static_cast<int32_t>(qd[0]); a.seq_q = static_cast<int32_t>(qd[1]);
     a.heads = static_cast<int32_t>(qd[2]); a.head_dim = static_cast<int32_t>(qd[3]);
     a.seq_kv = static_cast<int32_t>(kd[1]);
+    a.kv_heads = static_cast<int32_t>(kd[2]);          // fewer than heads: grouped-query attention
     ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.heads, a.seq_q, a.head_dim, a.q_strides);
-    ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.heads, a.seq_kv, a.head_dim, a.k_strides);
-    ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.heads, a.seq_kv, a.head_dim, a.v_strides);
+    ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.k_strides);
+    ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.v_strides);
     ahpc_fa_strides(AHPC_LAYOUT_BHSD, a.batch, a.heads, a.seq_q, a.head_dim, a.o_strides);
     a.scale = current_params_.scale_factor;
     a.causal = current_params_.causal_mask ? 1 : 0;
@@ -293,6 +296,7 @@ void PagedAttention::forward_batch(const std::vector<size_t>& sequence_ids, cons
     a.scale = current_params_.scale_factor;
     a.split_tokens = 0;
     a.stream = stream_;
+    a.q_heads = static_cast<int32_t>(H);
 
     bool all_host = true, contiguous = true;
     for (size_t i = 0; i < n; ++i) {

@@ -39,7 +39,8 @@ struct DecodeParams {
     const int32_t* seqs;       // device copy of the call's sequence slots
     float* part_o;             // [n_seqs][max_chunks][heads][head_dim]
     float2* part_ml;           // [n_seqs][max_chunks][heads]  (max, sum), base-2
-    int n_seqs, heads, head_dim, page_size, max_pages, max_chunks, split;
+    int n_seqs, heads, head_dim, page_size, max_pages, max_chunks, split;   // heads: query heads (q, out, partials)
+    int kv_heads, kv_group;    // heads of the pool; query head h reads key/value head h / kv_group
     size_t page_elems;
     float scale_log2;          // softmax scale * log2(e)
 };
@@ -107,7 +108,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(const DecodeP
     for (int pi = warp; pi < n_pages; pi += DEC_WARPS) {
         const int page = row[page0 + pi];
         if (page < 0) break;                                  // table shorter than the length says: stop (cuda_kernels.cu:419-420)
-        const size_t pbase = (size_t)page * p.page_elems + (size_t)head * PAGE * D;
+        const size_t pbase = (size_t)page * p.page_elems + (size_t)(head / p.kv_group) * PAGE * D;
         uint4 kreg[KP], vreg[SPG];
 #pragma unroll
         for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)(half * KP + j) * PAGE + slot) * 8);
@@ -218,7 +219,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_generic_kernel(const
         if (page >= 0) {
             s = 0.f;
             for (int piece = 0; piece < D / VEC; ++piece) {
-                const T* kp = kbase + k_piece_offset(p.page_elems, p.heads, PS, D, VEC, page, head, pos % PS, piece);
+                const T* kp = kbase + k_piece_offset(p.page_elems, p.kv_heads, PS, D, VEC, page, head / p.kv_group, pos % PS, piece);
                 for (int e = 0; e < VEC; ++e) s = fmaf(to_f32<T>(kp[e]), q_s[piece * VEC + e], s);
             }
         }
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_generic_kernel(const
             const int pos = tok0 + t;
             const int page = row[pos / PS];
             if (page < 0) break;
-            o = fmaf(sc[t], to_f32<T>(vbase[v_row_offset(p.page_elems, PS, D, page, head, pos % PS) + d]), o);
+            o = fmaf(sc[t], to_f32<T>(vbase[v_row_offset(p.page_elems, PS, D, page, head / p.kv_group, pos % PS) + d]), o);
         }
         p.part_o[pidx * D + d] = o;
     }
@@ -299,11 +300,22 @@ ScratchLayout scratch_layout(int n_seqs, int max_chunks, int heads, int head_dim
     return s;
 }
 
+// Query heads of a call: 0 means the pool's heads; otherwise a multiple of them (grouped-query attention).
+ahpc_status query_heads(const ahpc_decode_args* a, const char* who, int* out) {
+    const int kv = a->pool->cfg.heads;
+    const int qh = a->q_heads > 0 ? a->q_heads : kv;
+    if (a->q_heads < 0 || qh % kv != 0)
+        return fail(AHPC_INVALID_PARAMETERS, "%s: q_heads (%d) must be a multiple of the pool's heads (%d)", who, a->q_heads, kv);
+    if (qh > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "%s: at most 65535 heads", who);
+    *out = qh;
+    return AHPC_SUCCESS;
+}
+
 bool fast_path(const ahpc_pool* p) {
     return p->cfg.dtype != AHPC_F32 && p->cfg.page_size == 16 && (p->cfg.head_dim == 64 || p->cfg.head_dim == 128);
 }
 
-int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, int sms) {
+int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, int sms, int q_heads) {
     const int ps = p->cfg.page_size;
     if (requested > 0) return requested;
     int split = std::max(ps, 512 / ps * ps);
@@ -311,7 +323,7 @@ int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, in
     while (split / 2 >= 64 && (split / 2) % ps == 0) {
         int64_t ctas = 0;
         for (int i = 0; i < n; ++i) ctas += (p->h_len[seqs[i]] + split - 1) / split;
-        ctas *= p->cfg.heads;
+        ctas *= q_heads;
         if (ctas >= (int64_t)sms * 16) break;
         split /= 2;
     }
@@ -401,7 +413,8 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
     if (!a->seqs || !a->q || !a->out) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode: seqs, q and out must not be NULL");
     if (!dtype_valid(a->qo_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: unknown dtype %d", a->qo_dtype);
     if (a->n_seqs > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode: at most 65535 sequences per call");
-    if (p->cfg.heads > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode: at most 65535 heads");
+    int q_heads = 0;
+    AHPC_TRY(query_heads(a, "ahpc_paged_decode", &q_heads));
     std::lock_guard<std::mutex> lock(p->mu);
     ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     cudaStream_t st = (cudaStream_t)a->stream;
@@ -412,14 +425,14 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
         max_len = std::max(max_len, p->h_len[s]);
     }
     const int ps = p->cfg.page_size;
-    int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device));
+    int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device), q_heads);
     if (split % ps) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: split_tokens %d is not a multiple of the page size %d", split, ps);
     if (!fast_path(p) && split > GEN_MAX_SPLIT)
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: split_tokens %d exceeds %d for this pool configuration", split, GEN_MAX_SPLIT);
     const int max_chunks = std::max(1, (max_len + split - 1) / split);
     if (max_chunks > 2147483647 / 1) return fail(AHPC_INTERNAL_ERROR, "ahpc_paged_decode: chunk count overflow");
 
-    const ScratchLayout lay = scratch_layout(a->n_seqs, max_chunks, p->cfg.heads, p->cfg.head_dim);
+    const ScratchLayout lay = scratch_layout(a->n_seqs, max_chunks, q_heads, p->cfg.head_dim);
     if (p->scratch_bytes < lay.total) {
         if (p->scratch) { AHPC_CUDA_OK(cudaStreamSynchronize(st)); AHPC_CUDA_OK(cudaFree(p->scratch)); p->scratch = nullptr; p->scratch_bytes = 0; }
         size_t want = align_up(lay.total, size_t(1) << 20);
@@ -428,7 +441,7 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
     }
     char* sc = static_cast<char*>(p->scratch);
 
-    const size_t qo_bytes = (size_t)a->n_seqs * p->cfg.heads * p->cfg.head_dim * dtype_size(a->qo_dtype);
+    const size_t qo_bytes = (size_t)a->n_seqs * q_heads * p->cfg.head_dim * dtype_size(a->qo_dtype);
     const bool host_q = is_host_pointer(a->q), host_o = is_host_pointer(a->out);
     const void* dq = a->q;
     void* dout = a->out;
@@ -447,7 +460,8 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
     dp.seqs = reinterpret_cast<const int32_t*>(sc + lay.seqs_off);
     dp.part_ml = reinterpret_cast<float2*>(sc + lay.ml_off);
     dp.part_o = reinterpret_cast<float*>(sc + lay.o_off);
-    dp.n_seqs = a->n_seqs; dp.heads = p->cfg.heads; dp.head_dim = p->cfg.head_dim; dp.page_size = ps;
+    dp.n_seqs = a->n_seqs; dp.heads = q_heads; dp.head_dim = p->cfg.head_dim; dp.page_size = ps;
+    dp.kv_heads = p->cfg.heads; dp.kv_group = q_heads / p->cfg.heads;
     dp.max_pages = p->cfg.max_pages_per_seq; dp.max_chunks = max_chunks; dp.split = split;
     dp.page_elems = p->page_elems;
     const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);
@@ -472,7 +486,8 @@ ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* a) {
     if (!a->seqs || !a->q || !a->out) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode_static: seqs, q and out must not be NULL");
     if (!dtype_valid(a->qo_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: unknown dtype %d", a->qo_dtype);
     if (a->n_seqs > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode_static: at most 65535 sequences per call");
-    if (p->cfg.heads > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode_static: at most 65535 heads");
+    int q_heads = 0;
+    AHPC_TRY(query_heads(a, "ahpc_paged_decode_static", &q_heads));
     // Host tensors would need a staging buffer, i.e. an allocation: this entry point takes device memory only.
     if (is_host_pointer(a->q) || is_host_pointer(a->out))
         return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode_static: q and out must be device pointers (staging host tensors would allocate)");
@@ -486,12 +501,12 @@ ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* a) {
         max_len = std::max(max_len, p->h_len[s]);
     }
     const int ps = p->cfg.page_size;
-    const int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device));
+    const int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device), q_heads);
     if (split % ps) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: split_tokens %d is not a multiple of the page size %d", split, ps);
     if (!fast_path(p) && split > GEN_MAX_SPLIT)
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: split_tokens %d exceeds %d for this pool configuration", split, GEN_MAX_SPLIT);
     const int max_chunks = std::max(1, (max_len + split - 1) / split);
-    const ScratchLayout lay = scratch_layout(a->n_seqs, max_chunks, p->cfg.heads, p->cfg.head_dim);
+    const ScratchLayout lay = scratch_layout(a->n_seqs, max_chunks, q_heads, p->cfg.head_dim);
     if (lay.total > STATIC_SCRATCH_BYTES)
         return fail(AHPC_MEMORY_ALLOCATION_FAILED,
                     "ahpc_paged_decode_static: %d sequences x %d chunks of %d tokens need %zu bytes of split-KV scratch, the built-in "
@@ -509,7 +524,8 @@ ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* a) {
     dp.seqs = reinterpret_cast<const int32_t*>(sc + lay.seqs_off);
     dp.part_ml = reinterpret_cast<float2*>(sc + lay.ml_off);
     dp.part_o = reinterpret_cast<float*>(sc + lay.o_off);
-    dp.n_seqs = a->n_seqs; dp.heads = p->cfg.heads; dp.head_dim = p->cfg.head_dim; dp.page_size = ps;
+    dp.n_seqs = a->n_seqs; dp.heads = q_heads; dp.head_dim = p->cfg.head_dim; dp.page_size = ps;
+    dp.kv_heads = p->cfg.heads; dp.kv_group = q_heads / p->cfg.heads;
     dp.max_pages = p->cfg.max_pages_per_seq; dp.max_chunks = max_chunks; dp.split = split;
     dp.page_elems = p->page_elems;
     const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);

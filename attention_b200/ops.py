@@ -203,10 +203,12 @@ class KVPool:
         return f.value
 
     def decode(self, seqs, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, split_tokens=0, no_alloc=False):
-        """q: [n_seqs, heads, head_dim]; returns out of the same shape and dtype.  no_alloc=True goes
-        through ahpc_paged_decode_static (fixed built-in scratch, device tensors only)."""
+        """q: [n_seqs, q_heads, head_dim], q_heads a multiple of the pool's heads (grouped-query attention when
+        larger); returns out of the same shape and dtype.  no_alloc=True goes through ahpc_paged_decode_static
+        (fixed built-in scratch, device tensors only)."""
         seqs = _i32(seqs)
-        assert q.is_contiguous() and tuple(q.shape) == (seqs.size, self.heads, self.head_dim)
+        assert q.is_contiguous() and q.dim() == 3 and q.shape[0] == seqs.size and q.shape[2] == self.head_dim
+        assert q.shape[1] % self.heads == 0
         if out is None:
             out = torch.empty_like(q)
         assert out.is_contiguous() and out.shape == q.shape and out.dtype == q.dtype
@@ -214,6 +216,7 @@ class KVPool:
         a.pool, a.seqs, a.n_seqs = self._p, _pi32(seqs), seqs.size
         a.q, a.out, a.qo_dtype = q.data_ptr(), out.data_ptr(), _dtype_code(q)
         a.scale, a.split_tokens, a.stream = float(scale), int(split_tokens), self._stream()
+        a.q_heads = q.shape[1]
         fn = abi.lib().ahpc_paged_decode_static if no_alloc else abi.lib().ahpc_paged_decode
         abi.check(fn(C.byref(a)))
         return out

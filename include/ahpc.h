@@ -237,13 +237,16 @@ typedef struct ahpc_decode_args {
     ahpc_pool* pool;
     const int32_t* seqs;      /* host int32[n_seqs]: sequence slots, duplicates allowed     */
     int32_t n_seqs;
-    const void* q;            /* [n_seqs, heads, head_dim] in qo_dtype, contiguous          */
-    void* out;                /* [n_seqs, heads, head_dim] in qo_dtype, contiguous          */
+    const void* q;            /* [n_seqs, q_heads, head_dim] in qo_dtype, contiguous        */
+    void* out;                /* [n_seqs, q_heads, head_dim] in qo_dtype, contiguous        */
     int32_t qo_dtype;
     float scale;              /* 0 = 1/sqrt(head_dim) (paged_attention.cpp:634)             */
     int32_t split_tokens;     /* tokens per split-KV chunk; 0 = library default; must be a
                                  multiple of the page size                                  */
     void* stream;
+    int32_t q_heads;          /* query heads; 0 = the pool's heads.  A multiple of the pool's heads:
+                                 query head h reads key/value head h / (q_heads / heads)
+                                 (grouped-query attention, attention_interface.hpp:61)       */
 } ahpc_decode_args;
 
 AHPC_API ahpc_status ahpc_paged_decode(const ahpc_decode_args* args);

@@ -63,18 +63,21 @@ class Mirror:
         assert len(self.pool.free_ring()) == self.model.free_count()
         assert self.pool.error_flag() == 0
 
-    def decode_check(self, seqs, qo_dtype=None, split=0, host=False, scale=0.0):
+    def decode_check(self, seqs, qo_dtype=None, split=0, host=False, scale=0.0, group=1, no_alloc=False):
+        """group > 1: grouped-query attention, group query heads per key/value head of the pool; the oracle sees the
+        caches with every head repeated for the query heads that share it."""
         qo_dtype = qo_dtype or self.dtype
         n = len(seqs)
-        q = o.round_to(self.rng.standard_normal((n, self.H, self.D)).astype(np.float32), qo_dtype)
+        q = o.round_to(self.rng.standard_normal((n, self.H * group, self.D)).astype(np.float32), qo_dtype)
         tq = u.payload_to_torch(q, qo_dtype)
         if not host:
             tq = tq.to(DEV)
-        out = self.pool.decode(seqs, tq, split_tokens=split, scale=scale)
+        out = self.pool.decode(seqs, tq, split_tokens=split, scale=scale, no_alloc=no_alloc)
         table = np.stack([self.model.block_table(s) for s in seqs])
         lens = np.array([self.model.seq_len(s) for s in seqs], np.int32)
         sc = scale if scale else 1.0 / np.sqrt(self.D)
-        want = o.paged_decode(o.widen(q, qo_dtype), self.kc, self.vc, table, lens, sc)
+        kc, vc = (self.kc, self.vc) if group == 1 else (np.repeat(self.kc, group, axis=2), np.repeat(self.vc, group, axis=2))
+        want = o.paged_decode(o.widen(q, qo_dtype), kc, vc, table, lens, sc)
         u.assert_close(u.torch_to_f32(out), want, qo_dtype, f"decode lens={list(lens)} split={split}")
         return out
 
@@ -169,6 +172,20 @@ def test_decode_edge_context_lengths(dtype, D):
     m.decode_check(seqs, split=64)
     m.decode_check(seqs, split=1024)
     m.decode_check(seqs[::-1] + seqs[:2], host=True)      # any order, duplicates allowed
+
+
+@pytest.mark.parametrize("group", [2, 4, 8])
+@pytest.mark.parametrize("dtype,D,ps", [("f16", 128, 16), ("bf16", 64, 16), ("f32", 32, 8)])
+def test_decode_grouped_query_attention(group, dtype, D, ps):
+    """AttentionParams::key_value_heads (attention_interface.hpp:61) in the decode: group query heads read each
+    key/value head of the pool; fast path (16-bit, page 16) and general path; both decode entry points."""
+    m = Mirror(num_pages=40, heads=2, head_dim=D, dtype=dtype, page_size=ps, max_seqs=4, max_pages=16, seed=90 + group)
+    a, b, c = m.create(), m.create(), m.create()
+    m.append([a, b, c], [37, 1, 100])
+    m.decode_check([a, b, c], group=group)
+    m.decode_check([c, a], group=group, split=32 if ps == 16 else 16)
+    if dtype != "f32":
+        m.decode_check([b, c], group=group, no_alloc=True)
 
 
 def test_decode_empty_sequence_gives_zeros():
