@@ -182,6 +182,148 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(const DecodeP
     }
 }
 
+// Grouped-query fast path: the query heads of a group share a key/value head, and one CTA serves G of them, so a page
+// comes from HBM (and through L2) once for G query heads.  Same lane ownership as paged_decode_kernel; every key piece is
+// converted once and multiplied with the G queries from shared memory, every value row once with G weights.
+// grid (chunk, query heads / G, sequence); the group size p.kv_group is a multiple of G (a group of 8 takes two CTAs of
+// G = 4: measured faster than one CTA of 8, which runs out of registers and shared-memory bandwidth for the queries).
+// Partials are written per query head as the combine kernel expects them.
+template <typename T, typename TQ, int D, int G>
+__global__ void __launch_bounds__(DEC_THREADS) paged_decode_gqa_kernel(const DecodeParams p) {
+    constexpr int PAGE = 16;
+    constexpr int PIECES = D / 8;
+    constexpr int KP = PIECES / 2;
+    constexpr int LPR = PIECES;
+    constexpr int GROUPS = 32 / LPR;
+    constexpr int SPG = PAGE / GROUPS;
+
+    const int chunk = blockIdx.x, qh0 = blockIdx.y * G, kvh = qh0 / p.kv_group, si = blockIdx.z;
+    const int seq = p.seqs[si];
+    const int len = p.seq_len[seq];
+    const int tok0 = chunk * p.split;
+    if (tok0 >= len) return;
+    const int tok1 = min(len, tok0 + p.split);
+    const int page0 = tok0 / PAGE, n_pages = (tok1 - tok0 + PAGE - 1) / PAGE;
+
+    __shared__ __align__(16) float q_s[G][D];
+    __shared__ float sm_acc[DEC_WARPS][G][D];
+    __shared__ float sm_m[DEC_WARPS][G], sm_l[DEC_WARPS][G];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < G * D; i += DEC_THREADS)
+        q_s[i / D][i % D] = to_f32<TQ>(static_cast<const TQ*>(p.q)[((size_t)si * p.heads + qh0) * D + i]) * p.scale_log2;
+    __syncthreads();
+
+    const int slot = lane & 15, half = lane >> 4;
+    const int vcol = lane % LPR, vgrp = lane / LPR;
+    const T* kbase = static_cast<const T*>(p.k_data);
+    const T* vbase = static_cast<const T*>(p.v_data);
+    const int32_t* row = p.table + (size_t)seq * p.max_pages;
+
+    float m_run[G], l_part[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m_run[g] = -INFINITY;
+        l_part[g] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+    }
+
+    for (int pi = warp; pi < n_pages; pi += DEC_WARPS) {
+        const int page = row[page0 + pi];
+        if (page < 0) break;
+        const size_t pbase = (size_t)page * p.page_elems + (size_t)kvh * PAGE * D;
+        uint4 kreg[KP], vreg[SPG];
+#pragma unroll
+        for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)(half * KP + j) * PAGE + slot) * 8);
+#pragma unroll
+        for (int i = 0; i < SPG; ++i) vreg[i] = ld_stream(vbase + pbase + (size_t)(vgrp * SPG + i) * D + vcol * 8);
+
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[g] = 0.f;
+#pragma unroll
+        for (int j = 0; j < KP; ++j) {
+            float kf[8];
+            unpack8<T>(kreg[j], kf);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][(half * KP + j) * 8]);
+                const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][(half * KP + j) * 8 + 4]);
+                float t = s[g];
+                t = fmaf(kf[0], qa.x, t); t = fmaf(kf[1], qa.y, t); t = fmaf(kf[2], qa.z, t); t = fmaf(kf[3], qa.w, t);
+                t = fmaf(kf[4], qb.x, t); t = fmaf(kf[5], qb.y, t); t = fmaf(kf[6], qb.z, t); t = fmaf(kf[7], qb.w, t);
+                s[g] = t;
+            }
+        }
+        const bool past_end = tok0 + pi * PAGE + slot >= tok1;
+        float w[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float sg = s[g] + __shfl_xor_sync(0xffffffffu, s[g], 16);
+            if (past_end) sg = -INFINITY;
+            float pm = sg;
+#pragma unroll
+            for (int off = 8; off >= 1; off >>= 1) pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, off));
+            if (pm > m_run[g]) {                                  // warp-uniform
+                const float alpha = exp2f(m_run[g] - pm);         // m_run = -inf gives 0
+                l_part[g] *= alpha;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[g][e] *= alpha;
+                m_run[g] = pm;
+            }
+            w[g] = (sg == -INFINITY) ? 0.f : exp2f(sg - m_run[g]);
+            l_part[g] += w[g];
+        }
+#pragma unroll
+        for (int i = 0; i < SPG; ++i) {
+            float vf[8];
+            unpack8<T>(vreg[i], vf);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float wi = __shfl_sync(0xffffffffu, w[g], vgrp * SPG + i);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(wi, vf[e], acc[g][e]);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int off = 16; off >= LPR; off >>= 1)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+        float l_warp = l_part[g];
+#pragma unroll
+        for (int off = 8; off >= 1; off >>= 1) l_warp += __shfl_xor_sync(0xffffffffu, l_warp, off);
+        if (lane < LPR) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sm_acc[warp][g][lane * 8 + e] = acc[g][e];
+        }
+        if (lane == 0) { sm_m[warp][g] = m_run[g]; sm_l[warp][g] = l_warp; }
+    }
+    __syncthreads();
+
+    for (int i = tid; i < G * D; i += DEC_THREADS) {
+        const int g = i / D, d = i % D;
+        float m_all = sm_m[0][g];
+#pragma unroll
+        for (int wv = 1; wv < DEC_WARPS; ++wv) m_all = fmaxf(m_all, sm_m[wv][g]);
+        float o = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < DEC_WARPS; ++wv) o += sm_acc[wv][g][d] * exp2f(sm_m[wv][g] - m_all);
+        const size_t pidx = ((size_t)si * p.max_chunks + chunk) * p.heads + qh0 + g;
+        p.part_o[pidx * D + d] = o;
+        if (d == 0) {
+            float l = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < DEC_WARPS; ++wv) l += sm_l[wv][g] * exp2f(sm_m[wv][g] - m_all);
+            p.part_ml[pidx] = make_float2(m_all, l);
+        }
+    }
+}
+
 // General path: any pool type, page size and head_dim (multiple of the 16-byte piece).  One CTA per
 // (chunk, head, sequence): scores of the chunk into shared memory (a thread per token), block-wide
 // max and sum, then a thread per output dim.  split <= GEN_MAX_SPLIT.
@@ -311,11 +453,19 @@ ahpc_status query_heads(const ahpc_decode_args* a, const char* who, int* out) {
     return AHPC_SUCCESS;
 }
 
+bool fast_path(const ahpc_pool* p);
+int cta_heads(const ahpc_pool* p, int q_heads) {
+    const int group = q_heads / p->cfg.heads;
+    if (!fast_path(p)) return q_heads;
+    return group % 4 == 0 ? q_heads / 4 : group % 2 == 0 ? q_heads / 2 : q_heads;
+}
+
 bool fast_path(const ahpc_pool* p) {
     return p->cfg.dtype != AHPC_F32 && p->cfg.page_size == 16 && (p->cfg.head_dim == 64 || p->cfg.head_dim == 128);
 }
 
-int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, int sms, int q_heads) {
+// cta_heads: CTAs per (chunk, sequence) - query heads, or key/value heads when a grouped-query kernel serves a group per CTA
+int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, int sms, int cta_heads) {
     const int ps = p->cfg.page_size;
     if (requested > 0) return requested;
     int split = std::max(ps, 512 / ps * ps);
@@ -323,7 +473,7 @@ int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, in
     while (split / 2 >= 64 && (split / 2) % ps == 0) {
         int64_t ctas = 0;
         for (int i = 0; i < n; ++i) ctas += (p->h_len[seqs[i]] + split - 1) / split;
-        ctas *= q_heads;
+        ctas *= cta_heads;
         if (ctas >= (int64_t)sms * 16) break;
         split /= 2;
     }
@@ -336,8 +486,18 @@ ahpc_status launch_decode(const ahpc_pool* pool, const DecodeParams& dp, cudaStr
     bool launched = false;
     if constexpr (sizeof(T) == 2) {
         if (fast_path(pool)) {
-            if (dp.head_dim == 128) paged_decode_kernel<T, TQ, 128><<<grid, DEC_THREADS, 0, st>>>(dp);
+            // grouped-query kernels: one CTA per G query heads of a group
+#define AHPC_GQA_LAUNCH(G)                                                                                   \
+    do {                                                                                                     \
+        const dim3 ggrid(dp.max_chunks, dp.heads / G, dp.n_seqs);                                            \
+        if (dp.head_dim == 128) paged_decode_gqa_kernel<T, TQ, 128, G><<<ggrid, DEC_THREADS, 0, st>>>(dp);      \
+        else paged_decode_gqa_kernel<T, TQ, 64, G><<<ggrid, DEC_THREADS, 0, st>>>(dp);                          \
+    } while (0)
+            if (dp.kv_group % 4 == 0) AHPC_GQA_LAUNCH(4);
+            else if (dp.kv_group % 2 == 0) AHPC_GQA_LAUNCH(2);
+            else if (dp.head_dim == 128) paged_decode_kernel<T, TQ, 128><<<grid, DEC_THREADS, 0, st>>>(dp);   // other groups: a CTA per query head
             else paged_decode_kernel<T, TQ, 64><<<grid, DEC_THREADS, 0, st>>>(dp);
+#undef AHPC_GQA_LAUNCH
             launched = true;
         }
     }
@@ -425,7 +585,7 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
         max_len = std::max(max_len, p->h_len[s]);
     }
     const int ps = p->cfg.page_size;
-    int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device), q_heads);
+    int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device), cta_heads(p, q_heads));
     if (split % ps) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: split_tokens %d is not a multiple of the page size %d", split, ps);
     if (!fast_path(p) && split > GEN_MAX_SPLIT)
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: split_tokens %d exceeds %d for this pool configuration", split, GEN_MAX_SPLIT);
@@ -501,7 +661,7 @@ ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* a) {
         max_len = std::max(max_len, p->h_len[s]);
     }
     const int ps = p->cfg.page_size;
-    const int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device), q_heads);
+    const int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device), cta_heads(p, q_heads));
     if (split % ps) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: split_tokens %d is not a multiple of the page size %d", split, ps);
     if (!fast_path(p) && split > GEN_MAX_SPLIT)
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_static: split_tokens %d exceeds %d for this pool configuration", split, GEN_MAX_SPLIT);
