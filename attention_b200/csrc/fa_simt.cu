@@ -3,7 +3,7 @@
 // This is the exact-arithmetic kernel: every product and sum is FP32 (TF32 tensor cores cannot
 // meet a 1e-4 absolute tolerance), inputs of any supported storage type are widened on load and
 // the result is rounded to nearest even on store.  It also serves every case the tensor-core
-// kernel does not take: explicit [B,Sq,Skv] masks, head dimensions other than 64/128.
+// kernels do not take: head dimensions other than 64/128, strides a tensor map cannot express.
 //
 // It restates compute_multihead_attention / compute_attention_block of the reference
 // (src/algorithms/flash_attention.cpp:277-450) as intended, i.e. with the running (max, sum)

@@ -1,5 +1,6 @@
 // FlashAttention forward on the 5th-generation tensor cores (tcgen05, accumulators in TMEM),
-// for FP16 / BF16 inputs with head_dim 64 or 128.
+// for FP16 / BF16 inputs with head_dim 64 or 128, with the reference's optional [B,Sq,Skv] mask
+// (src/algorithms/flash_attention.cpp:596-607: 0 = masked, shared by the heads).
 //
 // It computes what FlashAttention::forward of the reference means to compute
 // (src/algorithms/flash_attention.cpp:68-112, 277-450): per (batch, head), tiles of
@@ -56,6 +57,8 @@ struct TcParams {
     int causal;
     int n_pairs;
     int kv_group;        // query heads per key/value head
+    const float* mask;   // optional [batch, seq_q, seq_kv], 0 = masked (flash_attention.cpp:596-607); shared by the heads
+    int mask_vec4;       // rows of the mask can be read as float4 (16-byte aligned base, seq_kv % 4 == 0)
     int* error_word;
     const int* redo;     // when set: per 128-row tile flags [batch*heads][tile slot]; only flagged pairs are computed
     int n_tiles;
@@ -278,6 +281,28 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     for (int i = 0; i < 32; ++i)
                         if (k0 + c * 32 + i > limit) sr[c][i] = 0xff800000u;            // -inf
             }
+            if (p.mask && row < p.seq_q) {
+                // explicit mask: this thread's row, the 128 keys of this tile
+                const float* mrow = p.mask + ((long long)b * p.seq_q + row) * p.seq_kv + k0;
+                if (p.mask_vec4 && k0 + BN <= p.seq_kv) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 m4 = __ldg(reinterpret_cast<const float4*>(mrow + c * 32 + i));
+                            if (m4.x == 0.f) sr[c][i] = 0xff800000u;
+                            if (m4.y == 0.f) sr[c][i + 1] = 0xff800000u;
+                            if (m4.z == 0.f) sr[c][i + 2] = 0xff800000u;
+                            if (m4.w == 0.f) sr[c][i + 3] = 0xff800000u;
+                        }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (k0 + c * 32 + i < p.seq_kv && __ldg(mrow + c * 32 + i) == 0.f) sr[c][i] = 0xff800000u;
+                }
+            }
             // row maximum: four independent chains of 3-input max
             float mx[4];
 #pragma unroll
@@ -468,7 +493,6 @@ bool fa_tc_supported(const FaLaunch& a, const char** why) {
     const char* r = nullptr;
     if (a.dtype != AHPC_F16 && a.dtype != AHPC_BF16) r = "inputs are not FP16/BF16";
     else if (a.head_dim != 64 && a.head_dim != 128) r = "head_dim is not 64 or 128";
-    else if (a.mask) r = "an explicit attention mask is given";
     else if (!(a.scale > 0.f)) r = "softmax scale is not positive";
     else if (!map_ok(a.q, a.qs) || !map_ok(a.k, a.ks) || !map_ok(a.v, a.vs)) r = "q/k/v are not 16-byte aligned with unit inner stride";
     else if (a.os[3] != 1 || reinterpret_cast<uintptr_t>(a.out) % 16 || a.os[0] % 8 || a.os[1] % 8 || a.os[2] % 8)
@@ -532,6 +556,8 @@ ahpc_status launch_two_tile(const FaLaunch& a, const int* redo, int* item_counte
     p.causal = a.causal;
     p.n_pairs = (a.seq_q + 2 * BM - 1) / (2 * BM);
     p.kv_group = a.heads / a.kv_heads;
+    p.mask = a.mask;
+    p.mask_vec4 = a.mask && reinterpret_cast<uintptr_t>(a.mask) % 16 == 0 && a.seq_kv % 4 == 0;
     p.n_tiles = (a.seq_q + BM - 1) / BM;
     p.redo = redo;
     p.item_counter = item_counter;
@@ -552,6 +578,9 @@ ahpc_status launch_fa_tc(const FaLaunch& a, int variant) {
     // have the exponent range of FP32, so its second pass has practically never anything to do; the two-tile kernel
     // for FP16, where scores that outgrow key tile 0's maximum by 2^15 would send tiles through both kernels.
     if (variant == AHPC_FA_KERNEL_TC) variant = a.dtype == AHPC_BF16 ? AHPC_FA_KERNEL_TC_DOUBLE_S : AHPC_FA_KERNEL_TC_TWO_TILE;
+    // An explicit mask goes to the two-tile kernel: its rescaling softmax copes with rows whose first key tiles are masked
+    // out entirely, where a reference maximum taken from key tile 0 would mean nothing.
+    if (a.mask) variant = AHPC_FA_KERNEL_TC_TWO_TILE;
     if (variant != AHPC_FA_KERNEL_TC_DOUBLE_S || tiles > REDO_RING_ENTRIES || tiles > 2147483647ll)
         return launch_two_tile(a, nullptr, nullptr);
     // double-buffered-score kernel, then the two-tile kernel over the tiles it flagged (normally none)

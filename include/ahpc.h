@@ -63,9 +63,9 @@ enum { AHPC_LAYOUT_BHSD = 0, AHPC_LAYOUT_BSHD = 1 };
 /* Kernel selection for ahpc_fa_fwd. */
 enum {
     AHPC_FA_KERNEL_AUTO = 0,   /* tensor-core kernel when the shape allows, else SIMT */
-    AHPC_FA_KERNEL_SIMT = 1,   /* FP32-FMA kernel (all dtypes, masks, any head_dim % 4 == 0 up to 256) */
-    AHPC_FA_KERNEL_TC = 2,     /* tcgen05/TMEM kernel (FP16/BF16, head_dim 64 or 128, no explicit mask): the library's
-                                  choice among the tensor-core kernels below */
+    AHPC_FA_KERNEL_SIMT = 1,   /* FP32-FMA kernel (all dtypes, any head_dim % 4 == 0 up to 256) */
+    AHPC_FA_KERNEL_TC = 2,     /* tcgen05/TMEM kernel (FP16/BF16, head_dim 64 or 128): the library's choice among the
+                                  tensor-core kernels below (an explicit mask always goes to the two-tile one) */
     AHPC_FA_KERNEL_TC_TWO_TILE = 3,  /* two 128-row query tiles per CTA, rescaling online softmax */
     AHPC_FA_KERNEL_TC_DOUBLE_S = 4   /* one query tile per CTA, score tile double-buffered, fixed reference maximum;
                                         followed by the two-tile kernel over the tiles it flagged (normally none) */

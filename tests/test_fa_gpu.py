@@ -88,6 +88,26 @@ def test_mask_half_and_fully_masked_rows(dtype):
     run_case(B, 3, S, S, 64, dtype, True, 9, mask=mask)
 
 
+@pytest.mark.parametrize("dtype,D", [("bf16", 128), ("f16", 64)])
+@pytest.mark.parametrize("S", [70, 256, 515])
+def test_mask_on_the_tensor_core_kernel(dtype, D, S):
+    """The reference's mask ([B,S,S] floats, 0 = masked, flash_attention.cpp:596-607; AttentionMaskTest masks the second
+    half of the keys) on the tcgen05 kernel: random masks, rows without any visible key, rows whose first key tiles are
+    masked out entirely, a key length that rules out 16-byte mask loads, alone and together with the causal mask."""
+    B = 2
+    rng = np.random.default_rng(S)
+    mask = (rng.random((B, S, S)) < 0.5).astype(np.float32)
+    mask[0, 5, :] = 0.0                                   # no visible key -> zeros
+    mask[1, 7, : S - 3] = 0.0                             # only the last three keys visible
+    mask[1, 9, S // 2 :] = 0.0                            # first half visible (the reference's AttentionMaskTest)
+    mask[1, 9, : S // 2] = 1.0
+    for causal in (False, True):
+        for kernel in (abi.KERNEL_AUTO, abi.KERNEL_TC_TWO_TILE, abi.KERNEL_TC_DOUBLE_S):
+            out = run_case(B, 3, S, S, D, dtype, causal, 9, mask=mask, kernel=kernel)
+            assert torch.all(out[0, :, 5, :] == 0)
+    assert _error_word() == 0
+
+
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_bshd_memory_order(dtype):
     run_case(2, 4, 100, 100, 64, dtype, True, 21, layout="BSHD")
@@ -164,7 +184,7 @@ def test_tc_is_the_default_for_16bit_and_bshd_views_work():
     t = torch.zeros((1, 2, 64, 128), dtype=torch.bfloat16, device=DEV)
     assert ops.select_kernel(t, t) == abi.KERNEL_TC
     assert ops.select_kernel(t.float(), t.float()) == abi.KERNEL_SIMT
-    assert ops.select_kernel(t, t, mask=True) == abi.KERNEL_SIMT
+    assert ops.select_kernel(t, t, mask=True) == abi.KERNEL_TC          # masks run on the tensor cores too
     run_case(2, 4, 300, 300, 128, "bf16", True, 33, layout="BSHD", kernel=abi.KERNEL_TC)
     run_case(2, 4, 300, 300, 64, "f16", False, 34, host=True)
     assert _error_word() == 0
