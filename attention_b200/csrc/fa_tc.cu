@@ -576,7 +576,8 @@ ahpc_status launch_fa_tc(const FaLaunch& a, int variant) {
     const long long tiles = (long long)((a.seq_q + BM - 1) / BM) * a.batch * a.heads;
     // The library's own choice (AHPC_FA_KERNEL_TC): the persistent double-buffered kernel for BF16, whose probabilities
     // have the exponent range of FP32, so its second pass has practically never anything to do; the two-tile kernel
-    // for FP16, where scores that outgrow key tile 0's maximum by 2^15 would send tiles through both kernels.
+    // for FP16, where scores beyond about +10 or rows entirely below about -4 (natural units) would send tiles through
+    // both kernels.
     if (variant == AHPC_FA_KERNEL_TC) variant = a.dtype == AHPC_BF16 ? AHPC_FA_KERNEL_TC_DOUBLE_S : AHPC_FA_KERNEL_TC_TWO_TILE;
     // An explicit mask goes to the two-tile kernel: its rescaling softmax copes with rows whose first key tiles are masked
     // out entirely, where a reference maximum taken from key tile 0 would mean nothing.

@@ -24,15 +24,16 @@
 // copied it to registers, and no softmax step waits for an MMA that depends on its own output: the
 // chain softmax(j) -> PV(j) -> S(j+1) -> softmax(j+1) of the two-tile kernel is gone.
 //
-// All groups feed one accumulator, so all probabilities of a row use ONE reference maximum: the row
-// maximum of key tile 0 (every query row sees key 0, so it is finite).  No other tile needs a row
-// maximum, which is what lets two warps share a row.  Using a reference below the true maximum is
-// exact as long as 2^(growth) stays inside the range of the 16-bit format of P (the final division
-// uses the row sum accumulated with the same reference).  A row whose scores later exceed the
-// reference by more than the format's margin (a tile's partial row sum reaching 2^15 for FP16, 2^64
-// for BF16) raises the item's entry in `redo`; the launcher always runs fa_tc.cu's kernel afterwards
-// over the same tiles, and that kernel recomputes exactly the flagged ones with its rescaling softmax
-// and returns at once for all others (it also puts the item counter back to zero).
+// No row maximum at all: the probabilities are 2^(scale * log2(e) * s) as they are.  Floating point is scale
+// invariant - P keeps its 8 (BF16) or 11 (FP16) significant bits whatever its magnitude, the row sum and O accumulate
+// in FP32, and the final division O / l cancels the common factor - so subtracting a maximum only matters for the
+// RANGE of the 16-bit format of P.  BF16 has the exponent range of FP32: rows whose largest score, in base-2 units,
+// lies between about -100 and +64 (-69 to +44 in natural units: any softmax input met in practice) are exact.
+// Outside that range (a tile's partial row sum reaching 2^64, or a row sum that underflows; for FP16: 2^15, or a row
+// sum below 2^-6) the row's item is flagged in `redo`; the launcher always runs fa_tc.cu's kernel afterwards over
+// the same tiles, and that kernel recomputes exactly the flagged ones with its rescaling softmax and returns at once
+// for all others (it also puts the item counter back to zero).  With no maximum, all key tiles are alike, any warp can
+// take any 64 columns of a row, and nothing is exchanged between warps except the four partial row sums at the end.
 //
 // Every wait is bounded, as in fa_tc.cu: a wait that gives up records a code in the device's error
 // word, raises the CTA's abort flag, every role leaves its loops, TMEM is released, the kernel returns.
@@ -92,7 +93,7 @@ struct Tc2Params {
 };
 
 #ifdef AHPC_TC2_STATS
-__device__ long long g_tc2_stats[256 * 8];      // experiment builds: per CTA {cycles, items, tiles, wait s_full, wait p_free, wait m_ready, wait item}
+__device__ long long g_tc2_stats[256 * 8];      // experiment builds: per CTA {cycles, items, tiles, wait s_full, wait p_free, -, wait item}
 #define STAT_T0() const long long st_t0_ = clock64()
 #define STAT_ADD(x) (x) += clock64() - st_t0_
 #else
@@ -102,15 +103,12 @@ __device__ long long g_tc2_stats[256 * 8];      // experiment builds: per CTA {c
 
 struct Aux2 {            // lives behind the tiles in shared memory
     uint64_t q_full[2], q_free[2], s_full[2], s_free[2], p_full[2], p_free[2], o_done, o_free;
-    uint64_t m_ready, m_taken, l_ready, l_taken, item_full[2], item_empty[2];
+    uint64_t l_ready, l_taken, item_full[2], item_empty[2];
     uint64_t k_full[6], k_empty[6], v_full[6], v_empty[6];
     uint32_t tmem_base;
     int abort;
     int item[2];         // the scheduler's two-entry queue of item numbers (-1: no more)
-    float m_ref[BM];     // reference maximum of each row of the current item, for the log-sum-exp output
-    // Row sums of the four softmax groups.  The first two rows of the array first carry the row maxima of an
-    // item's key tile 0 (left and right half of its columns); `m_taken` says that every group has read them,
-    // `l_taken` that every group has read the sums (so that the next item's maxima may overwrite them).
+    // Row sums of the four softmax groups on their way to the epilogue warps; `l_taken` says that those have read them.
     float l_part[4][BM];
 };
 static_assert(sizeof(Aux2) <= 3072, "Aux2 must fit its reserved bytes");
@@ -123,6 +121,8 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // A tile's partial row sum at or above this means some probability left the range reserved for P
     // (FP16 holds up to 65504; BF16 shares the exponent range of FP32, 2^64 leaves room for the sums).
     constexpr float GROW_SUM_LIMIT = BF16 ? 1.8446744e19f : 32768.0f;
+    // A whole row's sum below this means its probabilities sit at the bottom of P's range (or underflowed).
+    constexpr float ROW_SUM_FLOOR = BF16 ? 7.8886091e-31f /* 2^-100 */ : 0.015625f /* 2^-6 */;
     extern __shared__ __align__(1024) uint8_t smem_raw[];     // 128-byte-swizzled tiles need 1024-byte alignment
     const uint32_t smem_base = smem_u32(smem_raw);
     const uint32_t q_smem = smem_base;                                   // two buffers: item k uses buffer k & 1
@@ -146,8 +146,6 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         mbar_init(smem_u32(&aux->o_done), 1);
         mbar_init(smem_u32(&aux->o_free), 4);
-        mbar_init(smem_u32(&aux->m_ready), 8);
-        mbar_init(smem_u32(&aux->m_taken), SOFTMAX_WARPS);
         mbar_init(smem_u32(&aux->l_ready), SOFTMAX_WARPS);
         mbar_init(smem_u32(&aux->l_taken), 4);
         for (int s = 0; s < C::K_RING; ++s) {
@@ -356,9 +354,10 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             ok = wait_bounded(smem_u32(&aux->l_ready), k & 1, abort_flag, p.error_word, 1340);
             if (!ok) break;
             const float l_tot = (aux->l_part[0][r_in_tile] + aux->l_part[1][r_in_tile]) + (aux->l_part[2][r_in_tile] + aux->l_part[3][r_in_tile]);
-            const float m_ref = aux->m_ref[r_in_tile];
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&aux->l_taken));     // the next item's maxima may overwrite the sums
+            if (lane == 0) mbar_arrive(smem_u32(&aux->l_taken));     // the next item's sums may overwrite these
+            // out of P's range (a softmax warp stored +inf for a tile that overflowed): the second pass recomputes the item
+            if (row < p.seq_q && !(l_tot >= ROW_SUM_FLOOR && l_tot < 3.0e38f)) p.redo[w] = 1;
             ok = wait_bounded(smem_u32(&aux->o_done), k & 1, abort_flag, p.error_word, 1350);
             if (!ok) break;
             tc_fence_after_sync();
@@ -387,7 +386,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
             }
             if (p.lse && row < p.seq_q)
-                p.lse[((long long)it.b * p.heads + it.h) * p.seq_q + row] = l_tot > 0.f ? m_ref * p.scale + logf(l_tot) : -INFINITY;
+                p.lse[((long long)it.b * p.heads + it.h) * p.seq_q + row] = l_tot > 0.f ? logf(l_tot) : -INFINITY;
         }
     } else {
         // ------------------------------------------------------------------ softmax
@@ -404,6 +403,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #ifdef AHPC_TC2_STATS
         const long long st_start = clock64();
         long long st_items = 0, st_tiles = 0, st_s = 0, st_p = 0, st_m = 0, st_i = 0;
+        (void)st_m;
 #endif
 
         for (int k = 0; ok; ++k) {
@@ -413,9 +413,9 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const Item it = decode(w);
             const int row = it.q0 + r_in_tile;
             const int first_parity = t_base & 1;                 // the groups of this parity take key tile 0 of the item
-            float m_ref = 0.f, l_run = 0.f;
-            bool grew = false, have_m = false;
-            if (warp == 0 && lane == 0) p.redo[w] = 0;            // a row that outgrows the reference sets it below
+            float l_run = 0.f;
+            bool grew = false;
+            if (warp == 0 && lane == 0) p.redo[w] = 0;            // the epilogue warps set it when a row left P's range
 
             for (int j = g ^ first_parity; j < it.n_kv; j += 2, ++mine) {
                 { STAT_T0(); ok = wait_bounded(smem_u32(&aux->s_full[g]), mine & 1, abort_flag, p.error_word, 1300 + g); STAT_ADD(st_s); }
@@ -439,39 +439,13 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         for (int e = 0; e < 32; ++e)
                             if (k0 + c * 32 + e > limit) sr[c][e] = 0xff800000u;            // -inf
                 }
-                if (j == 0) {
-                    // Key tile 0 fixes the reference maximum of the row for all groups: its two halves meet in shared
-                    // memory, in rows of l_part that the previous item's epilogue may still be reading.
-                    if (k > 0) ok = wait_bounded(smem_u32(&aux->l_taken), (k - 1) & 1, abort_flag, p.error_word, 1310);
-                    if (!ok) break;
-                    float mx[2];
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        mx[c] = -INFINITY;
-#pragma unroll
-                        for (int e = 0; e < 32; e += 2) mx[c] = max3(mx[c], __uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
-                    }
-                    aux->l_part[hc][r_in_tile] = fmaxf(mx[0], mx[1]);
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&aux->m_ready));
-                }
-                if (!have_m) {
-                    { STAT_T0(); ok = wait_bounded(smem_u32(&aux->m_ready), k & 1, abort_flag, p.error_word, 1320); STAT_ADD(st_m); }
-                    if (!ok) break;
-                    m_ref = fmaxf(aux->l_part[0][r_in_tile], aux->l_part[1][r_in_tile]);
-                    if (hc == 0 && g == first_parity) aux->m_ref[r_in_tile] = m_ref;      // for the epilogue warps (log-sum-exp)
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&aux->m_taken));
-                    have_m = true;
-                }
-                const uint64_t negm2 = pack_f2(-m_ref * p.scale_log2, -m_ref * p.scale_log2);
                 uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};                                // four packed partial row sums
                 uint32_t packed[2][16];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
-                        const uint64_t x2 = fma2(pack_u2(sr[c][2 * e], sr[c][2 * e + 1]), scale2, negm2);
+                        const uint64_t x2 = mul2(pack_u2(sr[c][2 * e], sr[c][2 * e + 1]), scale2);
                         uint64_t p2;
                         if ((POLY_PATTERN >> (e & 7)) & 1u) {
                             p2 = poly_exp2_x2(x2);
@@ -493,7 +467,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 tmem_st16(p_addr + 16, packed[1]);
                 const uint64_t tot = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
                 const float psum = __uint_as_float((uint32_t)tot) + __uint_as_float((uint32_t)(tot >> 32));
-                // A probability beyond the range reserved for P means the reference maximum is too stale for this row.
+                // A probability beyond the range reserved for P: the item has to go through the second pass.
                 grew |= !(psum < GROW_SUM_LIMIT);
                 l_run += psum;
                 tmem_wait_st();
@@ -503,16 +477,11 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
             if (!ok) break;
 
-            // The row sums of the four groups meet in shared memory, in the array that carried the maxima of key tile 0:
-            // first make sure every group has taken those.
-            if (!have_m) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&aux->m_taken));
-            }
-            ok = wait_bounded(smem_u32(&aux->m_taken), k & 1, abort_flag, p.error_word, 1335);
+            // The row sums of the four groups go to the epilogue warps through shared memory, once those have read the
+            // previous item's.  An overflow travels as +inf: the epilogue warps flag the item.
+            if (k > 0) ok = wait_bounded(smem_u32(&aux->l_taken), (k - 1) & 1, abort_flag, p.error_word, 1336);
             if (!ok) break;
-            if (grew) p.redo[w] = 1;           // behind warp 0's "0" of this item: the wait above orders the two stores
-            aux->l_part[wg][r_in_tile] = l_run;
+            aux->l_part[wg][r_in_tile] = grew ? INFINITY : l_run;
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&aux->l_ready));     // the epilogue warps take it from here
             t_base += it.n_kv;

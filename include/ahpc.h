@@ -67,8 +67,9 @@ enum {
     AHPC_FA_KERNEL_TC = 2,     /* tcgen05/TMEM kernel (FP16/BF16, head_dim 64 or 128): the library's choice among the
                                   tensor-core kernels below (an explicit mask always goes to the two-tile one) */
     AHPC_FA_KERNEL_TC_TWO_TILE = 3,  /* two 128-row query tiles per CTA, rescaling online softmax */
-    AHPC_FA_KERNEL_TC_DOUBLE_S = 4   /* one query tile per CTA, score tile double-buffered, fixed reference maximum;
-                                        followed by the two-tile kernel over the tiles it flagged (normally none) */
+    AHPC_FA_KERNEL_TC_DOUBLE_S = 4   /* persistent kernel, one query tile per item, score tile double-buffered, softmax
+                                        without a row maximum (exact inside the exponent range of P); followed by the
+                                        two-tile kernel over the tiles it flagged as out of range (normally none) */
 };
 
 /* ------------------------------------------------------------------------------------------

@@ -211,6 +211,26 @@ def test_tc_large_scores_exercise_the_rescale_paths(kernel, dtype, q_scale, k_to
     assert _error_word() == 0
 
 
+@pytest.mark.parametrize("kernel", TC_VARIANTS)
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("offset", [1.0, 2.3, 3.2])
+def test_tc_scores_far_below_zero(kernel, dtype, offset):
+    """Every score of every row strongly negative (about -11, -60 and -115 in natural units): the kernel without a row
+    maximum works at the bottom of the range of P, or flags its tiles for the second pass when even FP32 underflows."""
+    B, H, S, D = 1, 2, 384, 128
+    rng = np.random.default_rng(5)
+    q = o.widen(o.round_to(offset + 0.05 * rng.standard_normal((B, H, S, D)).astype(np.float32), dtype), dtype)
+    k = o.widen(o.round_to(-offset + 0.05 * rng.standard_normal((B, H, S, D)).astype(np.float32), dtype), dtype)
+    v = o.widen(o.round_to(rng.standard_normal((B, H, S, D)).astype(np.float32), dtype), dtype)
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    tq, tk, tv = (torch.from_numpy(x).to(tdt).to(DEV) for x in (q, k, v))
+    for causal in (False, True):
+        want = o.attention_fwd(q, k, v, 1 / np.sqrt(D), causal)
+        out = ops.flash_attention_forward(tq, tk, tv, causal=causal, kernel=kernel)
+        u.assert_close(u.torch_to_f32(out), want, dtype, f"scores near {-offset * offset * np.sqrt(D):.0f}")
+    assert _error_word() == 0
+
+
 def test_tc_lse():
     B, H, S, D = 1, 2, 300, 64
     (q, k, v), (tq, tk, tv) = u.rounded_inputs((B, H, S, D), "f16", 41)
