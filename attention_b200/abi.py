@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = [
     "ahpc_pool_live_seqs", "ahpc_pool_read_block_table", "ahpc_pool_read_seq_lens",
     "ahpc_pool_read_refcounts", "ahpc_pool_read_free_ring", "ahpc_pool_read_error_flag",
     "ahpc_paged_decode", "ahpc_paged_decode_scratch_bytes", "ahpc_paged_decode_static",
-    "ahpc_paged_decode_static_capacity", "ahpc_shard_range",
+    "ahpc_paged_decode_static_capacity", "ahpc_paged_prefill", "ahpc_shard_range",
 ]
 
 
@@ -68,6 +68,14 @@ class DecodeArgs(C.Structure):
         ("pool", C.c_void_p), ("seqs", C.POINTER(C.c_int32)), ("n_seqs", C.c_int32),
         ("q", C.c_void_p), ("out", C.c_void_p), ("qo_dtype", C.c_int32), ("scale", C.c_float),
         ("split_tokens", C.c_int32), ("stream", C.c_void_p), ("q_heads", C.c_int32),
+    ]
+
+
+class PrefillArgs(C.Structure):
+    _fields_ = [
+        ("pool", C.c_void_p), ("seqs", C.POINTER(C.c_int32)), ("n_query", C.POINTER(C.c_int32)), ("n_seqs", C.c_int32),
+        ("q", C.c_void_p), ("out", C.c_void_p), ("qo_dtype", C.c_int32), ("q_heads", C.c_int32), ("scale", C.c_float),
+        ("causal", C.c_int32), ("stream", C.c_void_p), ("head_major", C.c_int32),
     ]
 
 
@@ -135,6 +143,7 @@ def lib() -> C.CDLL:
     L.ahpc_paged_decode_static_capacity.restype = C.c_size_t
     L.ahpc_paged_decode_scratch_bytes.argtypes = [vp, i32, i32, i32]
     L.ahpc_paged_decode_scratch_bytes.restype = C.c_size_t
+    L.ahpc_paged_prefill.argtypes = [C.POINTER(PrefillArgs)]
     L.ahpc_shard_range.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]
     _lib = L
     return L

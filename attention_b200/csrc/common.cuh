@@ -94,6 +94,7 @@ struct FaLaunch {                 // validated, device-pointer form of ahpc_fa_a
     int64_t qs[4], ks[4], vs[4], os[4];
     float scale;
     int causal;
+    int causal_offset = 0;        // causal rule: query row r stands at position r + causal_offset (0 for the public dense call)
     int device;
     cudaStream_t stream;
 };
@@ -103,5 +104,28 @@ ahpc_status launch_fa_tc2(const FaLaunch& a, int* redo_flags, int* item_counter)
 int fa_tc2_bh_group(const FaLaunch& a);                                              // fa_tc2.cu: group size of its item order
 bool fa_tc_supported(const FaLaunch& a, const char** why);
 ahpc_status fa_tc_read_error_word(int device, int* out);   // fa_tc.cu
+
+// Attention of query rows over K/V held in a paged pool (fa_tc.cu, called from paged_prefill.cu).
+struct PagedPrefillLaunch {
+    const void* q;                // total_q rows of q_heads heads, see the strides
+    void* out;                    // same shape
+    int dtype;                    // of q, out and the pool
+    int q_heads, kv_heads, head_dim, page_size;
+    long long token_stride, head_stride;   // of q and out, in elements
+    long long total_q;            // rows of q / out
+    int max_q;                    // longest run of query rows of one sequence
+    int n_seqs;
+    const int4* seqs_dev;         // device: per listed sequence {slot, first row in q/out, query rows, tokens held}
+    const void *k_data, *v_data;  // the pool's storage
+    const int32_t* table;
+    long long page_elems;
+    int num_pages, max_pages;
+    float scale;
+    int causal;
+    int device;
+    cudaStream_t stream;
+};
+bool fa_paged_tc_supported(const PagedPrefillLaunch& a, const char** why);
+ahpc_status launch_fa_paged_tc(const PagedPrefillLaunch& a);
 
 }  // namespace ahpc

@@ -41,6 +41,7 @@ struct SimtParams {
     int64_t qs[4], ks[4], vs[4], os[4];
     float scale;
     int causal;
+    int causal_offset;       // query row r stands at position r + causal_offset
 };
 
 template <typename T, int DP>
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(NTHREADS) fa_fwd_simt_kernel(const SimtParams 
     int n_tiles = (p.seq_kv + BK - 1) / BK;
     if (p.causal) {
         // keys beyond the last query row of this tile are all masked
-        int last_q = min(q0 + BQ, p.seq_q) - 1;
+        int last_q = min(q0 + BQ, p.seq_q) - 1 + p.causal_offset;
         n_tiles = min(n_tiles, last_q / BK + 1);
     }
 
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(NTHREADS) fa_fwd_simt_kernel(const SimtParams 
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int kj = k0 + tx * 4 + j;
-                bool visible = qi < p.seq_q && kj < p.seq_kv && !(p.causal && qi < kj);
+                bool visible = qi < p.seq_q && kj < p.seq_kv && !(p.causal && qi + p.causal_offset < kj);
                 if (visible && p.mask) visible = p.mask[((int64_t)b * p.seq_q + qi) * p.seq_kv + kj] != 0.0f;
                 s[i][j] = visible ? s[i][j] * p.scale : -INFINITY;
                 row_max = fmaxf(row_max, s[i][j]);
@@ -217,7 +218,7 @@ ahpc_status launch_fa_simt(const FaLaunch& a) {
     p.batch = a.batch; p.heads = a.heads; p.seq_q = a.seq_q; p.seq_kv = a.seq_kv; p.head_dim = a.head_dim;
     p.kv_group = a.heads / a.kv_heads;
     for (int i = 0; i < 4; ++i) { p.qs[i] = a.qs[i]; p.ks[i] = a.ks[i]; p.vs[i] = a.vs[i]; p.os[i] = a.os[i]; }
-    p.scale = a.scale; p.causal = a.causal;
+    p.scale = a.scale; p.causal = a.causal; p.causal_offset = a.causal_offset;
     switch (a.dtype) {
         case AHPC_F32: return launch_for_dim<float>(p, a.stream);
         case AHPC_F16: return launch_for_dim<__half>(p, a.stream);

@@ -48,6 +48,15 @@ template <int D> struct Cfg {
     static constexpr uint32_t O_COL = 256;                   // first column of O0
 };
 
+// K/V held in a paged pool (pool.cuh) instead of dense tensors: what the kernel needs to walk the pages.
+struct PagedView {
+    const uint16_t* k_data;   // keys: [page][head][2 groups of 8 slots][head_dim/8][8 slots][8 elements]
+    const int32_t* table;     // block table [max_seqs][max_pages]
+    const int4* seqs;         // per listed sequence {slot, first query row in q/out, query rows, tokens held}
+    long long page_elems;     // elements of K (or V) in one page
+    int max_pages;
+};
+
 struct TcParams {
     void* out;
     float* lse;
@@ -55,6 +64,7 @@ struct TcParams {
     long long os[4];
     float scale, scale_log2;
     int causal;
+    int causal_offset;   // dense: query row r stands at position r + causal_offset for the causal rule
     int n_pairs;
     int kv_group;        // query heads per key/value head
     const float* mask;   // optional [batch, seq_q, seq_kv], 0 = masked (flash_attention.cpp:596-607); shared by the heads
@@ -64,6 +74,7 @@ struct TcParams {
     int n_tiles;
     int bh_group;        // group size of fa_fwd_tc2_kernel's item order (ItemOrder), for the flag lookup
     int* item_counter;   // when set: the item counter of the preceding fa_fwd_tc2_kernel launch, put back to zero here
+    PagedView paged;     // used by the PAGED instantiation only
 };
 
 struct Barriers {        // one uint64 each, in shared memory
@@ -72,11 +83,22 @@ struct Barriers {        // one uint64 each, in shared memory
     int abort;
 };
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool PAGED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const TcParams p) {
     using C = Cfg<D>;
+    // Dense: the sizes of the call.  Paged: those of the sequence this CTA works on (grid.z), whose queries are its LAST
+    // seq_q tokens: query row r sits at position r + c_off, which is what the causal rule compares with the key index.
+    int seq_q = p.seq_q, seq_kv = p.seq_kv, c_off = p.causal_offset, row_base = 0, n_pairs = p.n_pairs;
+    const int32_t* table_row = nullptr;
+    if constexpr (PAGED) {
+        const int4 info = p.paged.seqs[blockIdx.z];
+        seq_q = info.z; seq_kv = info.w; c_off = seq_kv - seq_q; row_base = info.y;
+        n_pairs = (seq_q + 2 * BM - 1) / (2 * BM);
+        table_row = p.paged.table + (long long)info.x * p.paged.max_pages;
+        if ((int)blockIdx.x >= n_pairs) return;          // the grid is sized for the longest query run of the call
+    }
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -87,7 +109,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    const int total_pairs = p.n_pairs * p.batch * p.heads;
+    const int total_pairs = PAGED ? n_pairs : p.n_pairs * p.batch * p.heads;
     // second pass: did fa_fwd_tc2_kernel flag a tile of this pair?
     auto flagged = [&](int work) {
         const int bh_w = work / p.n_pairs, slot_w = work % p.n_pairs;
@@ -126,13 +148,14 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (work >= total_pairs) break;
     // Consecutive work numbers are the pairs of ONE (batch, head), so the CTAs resident at any time share a few K/V
     // streams and those stay in L2; heavy (late) pairs first when causal.
-    const int bh = work / p.n_pairs, pair_slot = work % p.n_pairs;
-    const int pair = p.causal ? p.n_pairs - 1 - pair_slot : pair_slot;
-    const int b = bh / p.heads, h = bh % p.heads;
+    const int bh = PAGED ? (int)blockIdx.y : work / p.n_pairs, pair_slot = PAGED ? work : work % p.n_pairs;
+    const int pair = p.causal ? n_pairs - 1 - pair_slot : pair_slot;
+    const int b = PAGED ? 0 : bh / p.heads, h = PAGED ? bh : bh % p.heads;
     const int q0 = pair * 2 * BM;
-    const int n_t0 = kv_tiles_for(q0, p.seq_q, p.seq_kv, p.causal);
-    const int n_t1 = kv_tiles_for(q0 + BM, p.seq_q, p.seq_kv, p.causal);
+    const int n_t0 = kv_tiles_for(q0, seq_q, seq_kv, p.causal, c_off);
+    const int n_t1 = kv_tiles_for(q0 + BM, seq_q, seq_kv, p.causal, c_off);
     const int n_kv = max(n_t0, n_t1);
+    const int n_pages = (seq_kv + 15) >> 4;                  // paged: pages of the sequence (16 tokens each)
 
     if (threadIdx.x == MMA_WARP * 32) {
         for (int t = 0; t < 2; ++t) {
@@ -155,17 +178,48 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             prefetch_tensormap(&map_q);
-            prefetch_tensormap(&map_k);
+            if constexpr (!PAGED) prefetch_tensormap(&map_k);
             prefetch_tensormap(&map_v);
             for (int t = 0; t < 2; ++t) {
                 if ((t == 0 ? n_t0 : n_t1) == 0) continue;
                 const uint32_t bar = smem_u32(&bars->q[t]);
                 mbar_expect_tx(bar, C::TILE_BYTES);
                 for (int sub = 0; sub < C::SUBTILES; ++sub)
-                    tma_load_4d(q_smem + t * C::TILE_BYTES + sub * C::SUB_BYTES, &map_q, bar, sub * 64, q0 + t * BM, h, b);
+                    tma_load_4d(q_smem + t * C::TILE_BYTES + sub * C::SUB_BYTES, &map_q, bar, sub * 64, row_base + q0 + t * BM, h, b);
             }
-            int issued = 0;
-            bool ok = true;
+        }
+        int issued = 0;
+        bool ok = true;
+        if constexpr (PAGED) {
+            // The whole warp walks the ring; lane i brings page i of the tile: one bulk copy of the page's contiguous
+            // block of keys for this head (which lies in the pool in the form the MMA reads, see issue_s), or one box
+            // per 128-byte column block of its values.  Pages past the end of the sequence are not copied: their keys
+            // are masked and their part of P V is never issued.
+            constexpr uint32_t PAGE_BYTES = 16 * D * 2;
+            const int kvh = h / p.kv_group;
+            int page = 0;
+            for (int idx = 0; idx < 2 * n_kv; ++idx) {
+                const int slot = idx % C::STAGES, round = idx / C::STAGES;
+                if (round > 0) ok = wait_bounded(smem_u32(&bars->empty[slot]), (round - 1) & 1, abort_flag, p.error_word, 100 + slot);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint32_t bar = smem_u32(&bars->full[slot]);
+                const int first = (idx >> 1) * (BN / 16), valid = min(BN / 16, n_pages - first);
+                if (lane == 0) mbar_expect_tx(bar, valid * PAGE_BYTES);
+                if (idx & 1) {
+                    if (lane < valid)
+                        for (int sub = 0; sub < C::SUBTILES; ++sub)
+                            tma_load_4d(ring_smem + slot * C::TILE_BYTES + sub * C::SUB_BYTES + lane * 16 * 128, &map_v, bar, sub * 64, 0, kvh, page);
+                } else {
+                    if (lane < valid) {
+                        page = __ldg(table_row + first + lane);                  // the value tile that follows uses the same pages
+                        bulk_load(ring_smem + slot * C::TILE_BYTES + lane * PAGE_BYTES,
+                                  p.paged.k_data + (long long)page * p.paged.page_elems + (long long)kvh * 16 * D, PAGE_BYTES, bar);
+                    }
+                }
+                issued = idx + 1;
+            }
+        } else if (lane == 0) {
             for (int idx = 0; idx < 2 * n_kv && ok; ++idx) {
                 const int slot = idx % C::STAGES, round = idx / C::STAGES;
                 if (round > 0) ok = wait_bounded(smem_u32(&bars->empty[slot]), (round - 1) & 1, abort_flag, p.error_word, 100 + slot);
@@ -177,13 +231,13 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     tma_load_4d(ring_smem + slot * C::TILE_BYTES + sub * C::SUB_BYTES, map, bar, sub * 64, (idx >> 1) * BN, h / p.kv_group, b);
                 issued = idx + 1;
             }
-            if (!ok) {
-                // Leave no copy in flight: wait (bounded) for the loads of the last ring round issued.
-                for (int idx = max(0, issued - C::STAGES); idx < issued; ++idx) {
-                    const int slot = idx % C::STAGES, round = idx / C::STAGES;
-                    long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&bars->full[slot]), round & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
-                }
+        }
+        if (!ok && lane == 0) {
+            // Leave no copy in flight: wait (bounded) for the loads of the last ring round issued.
+            for (int idx = max(0, issued - C::STAGES); idx < issued; ++idx) {
+                const int slot = idx % C::STAGES, round = idx / C::STAGES;
+                long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&bars->full[slot]), round & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
             }
         }
     } else if (warp == MMA_WARP) {
@@ -200,17 +254,24 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * C::SUB_BYTES + (kk & 3) * 32;
-                    mma_ss(tmem + t * BN, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), IDESC_S, kk > 0);
+                    if constexpr (PAGED) {
+                        // Keys as the pool keeps them, [8-slot group][piece][8 slots][16 bytes] per page: 8-key x 16-byte core
+                        // matrices, the two pieces of a step 128 bytes apart, the 16 key groups of the tile head_dim*16 apart.
+                        mma_ss(tmem + t * BN, smem_desc_sw128(qa + off, 16, 1024), smem_desc_plain(ka + kk * 256, 128, D * 16), IDESC_S, kk > 0);
+                    } else {
+                        mma_ss(tmem + t * BN, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), IDESC_S, kk > 0);
+                    }
                 }
                 tc_commit(smem_u32(&bars->s[t]));
             };
             // O_t (+)= P_t V_j : 8 MMAs of K = 16 keys; V is MN-major (head_dim contiguous)
-            auto issue_o = [&](int t, int slot, bool first) {
+            auto issue_o = [&](int t, int slot, bool first, int steps) {
                 const uint32_t va = ring_smem + slot * C::TILE_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)
-                    mma_ts(tmem + C::O_COL + t * D, tmem + t * BN + kk * 8, smem_desc_sw128(va + kk * 16 * 128, C::SUB_BYTES, 1024),
-                           IDESC_O, !(first && kk == 0));
+                    if (!PAGED || kk < steps)            // paged: one step per page held
+                        mma_ts(tmem + C::O_COL + t * D, tmem + t * BN + kk * 8, smem_desc_sw128(va + kk * 16 * 128, C::SUB_BYTES, 1024),
+                               IDESC_O, !(first && kk == 0));
                 tc_commit(smem_u32(&bars->o[t]));
             };
 
@@ -234,7 +295,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         ok = wait_bounded(smem_u32(&bars->p[t]), j & 1, abort_flag, p.error_word, 240 + t);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        issue_o(t, slot_v, j == 0);
+                        issue_o(t, slot_v, j == 0, min(BN / 16, n_pages - j * (BN / 16)));
                     }
                     if (j + 1 < n_t[t]) issue_s(t, slot_k);
                 }
@@ -272,16 +333,30 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             tmem_wait_ld();
 
             const int k0 = j * BN;
-            const bool need_mask = (p.causal && k0 + BN - 1 > q0 + t * BM) || (k0 + BN > p.seq_kv);
+            const bool need_mask = (p.causal && k0 + BN - 1 > q0 + t * BM + c_off) || (k0 + BN > seq_kv);
             if (need_mask) {
-                const int limit = p.causal ? min(p.seq_kv - 1, row) : p.seq_kv - 1;     // last visible key
+                const int limit = p.causal ? min(seq_kv - 1, row + c_off) : seq_kv - 1;     // last visible key
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (k0 + c * 32 + i > limit) sr[c][i] = 0xff800000u;            // -inf
+                for (int k = 0; k < BN; ++k)
+                    if (k0 + k > limit) sr[k >> 5][k & 31] = 0xff800000u;            // -inf
             }
-            if (p.mask && row < p.seq_q) {
+            if constexpr (PAGED) {
+                // The sequence's last page may hold slots nobody wrote: their probabilities are zero, but zero times
+                // whatever bits lie there need not be zero.  Clear those value rows in shared memory before P V reads them.
+                if (k0 + BN > seq_kv && (seq_kv & 15)) {
+                    const int idx_v = 2 * j + 1, slot_v = idx_v % C::STAGES;
+                    ok = wait_bounded(smem_u32(&bars->full[slot_v]), (idx_v / C::STAGES) & 1, abort_flag, p.error_word, 320 + t);
+                    if (!ok) break;
+                    const int first_row = seq_kv - k0, rows = 16 - (seq_kv & 15);
+                    uint8_t* vt = smem_aligned + 2 * C::TILE_BYTES + slot_v * C::TILE_BYTES;
+                    for (int c = r_in_tile; c < rows * (D / 8); c += BM) {
+                        const int r = first_row + c / (D / 8), piece = c % (D / 8);
+                        *reinterpret_cast<uint4*>(vt + (piece >> 3) * C::SUB_BYTES + r * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    fence_proxy_async();
+                }
+            }
+            if (!PAGED && p.mask && row < p.seq_q) {
                 // explicit mask: this thread's row, the 128 keys of this tile
                 const float* mrow = p.mask + ((long long)b * p.seq_q + row) * p.seq_kv + k0;
                 if (p.mask_vec4 && k0 + BN <= p.seq_kv) {
@@ -368,13 +443,13 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (ok && n_mine > 0) {
             tc_fence_after_sync();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            uint16_t* orow_g = static_cast<uint16_t*>(p.out) + b * p.os[0] + h * p.os[1] + (long long)row * p.os[2];
+            uint16_t* orow_g = static_cast<uint16_t*>(p.out) + b * p.os[0] + h * p.os[1] + (long long)(row_base + row) * p.os[2];
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t orow[32];
                 tmem_ld32(o_addr + c * 32, orow);      // warp-collective: rows past seq_q still take part
                 tmem_wait_ld();
-                if (row < p.seq_q) {
+                if (row < seq_q) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint4 v;
@@ -386,7 +461,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     }
                 }
             }
-            if (p.lse && row < p.seq_q)
+            if (!PAGED && p.lse && row < p.seq_q)
                 p.lse[((long long)b * p.heads + h) * p.seq_q + row] =
                     l_run > 0.f ? m_used * p.scale + logf(l_run) : -INFINITY;
         }
@@ -404,7 +479,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 template <int D, bool BF16>
 ahpc_status launch(const FaLaunch& a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcParams& p) {
     using C = Cfg<D>;
-    auto kernel = fa_fwd_tc_kernel<D, BF16>;
+    auto kernel = fa_fwd_tc_kernel<D, BF16, false>;
     AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
     long long ctas = (long long)p.n_pairs * a.batch * a.heads;
     if (p.redo) ctas = std::min<long long>(ctas, std::max(1, sm_count(a.device)));      // second pass: one CTA per SM walks the flags
@@ -547,13 +622,14 @@ ahpc_status launch_two_tile(const FaLaunch& a, const int* redo, int* item_counte
     AHPC_TRY(make_map(&mq, a.q, a.dtype, a.batch, a.heads, a.seq_q, a.head_dim, a.qs));
     AHPC_TRY(make_map(&mk, a.k, a.dtype, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.ks));
     AHPC_TRY(make_map(&mv, a.v, a.dtype, a.batch, a.kv_heads, a.seq_kv, a.head_dim, a.vs));
-    TcParams p;
+    TcParams p{};
     p.out = a.out; p.lse = a.lse;
     p.batch = a.batch; p.heads = a.heads; p.seq_q = a.seq_q; p.seq_kv = a.seq_kv;
     for (int i = 0; i < 4; ++i) p.os[i] = a.os[i];
     p.scale = a.scale;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.causal = a.causal;
+    p.causal_offset = a.causal_offset;
     p.n_pairs = (a.seq_q + 2 * BM - 1) / (2 * BM);
     p.kv_group = a.heads / a.kv_heads;
     p.mask = a.mask;
@@ -570,6 +646,61 @@ ahpc_status launch_two_tile(const FaLaunch& a, const int* redo, int* item_counte
 
 }  // namespace
 
+template <int D, bool BF16>
+ahpc_status launch_paged(const PagedPrefillLaunch& a, const CUtensorMap& mq, const CUtensorMap& mv, const TcParams& p) {
+    using C = Cfg<D>;
+    auto kernel = fa_fwd_tc_kernel<D, BF16, true>;
+    AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
+    const dim3 grid((unsigned)((a.max_q + 2 * BM - 1) / (2 * BM)), (unsigned)a.q_heads, (unsigned)a.n_seqs);
+    kernel<<<grid, TC_THREADS, C::SMEM_BYTES, a.stream>>>(mq, mq /*no dense key map*/, mv, p);
+    AHPC_CUDA_OK(cudaGetLastError());
+    return AHPC_SUCCESS;
+}
+
+bool fa_paged_tc_supported(const PagedPrefillLaunch& a, const char** why) {
+    const char* r = nullptr;
+    if (a.dtype != AHPC_F16 && a.dtype != AHPC_BF16) r = "pool and queries are not both FP16 or both BF16";
+    else if (a.head_dim != 64 && a.head_dim != 128) r = "head_dim is not 64 or 128";
+    else if (a.page_size != 16) r = "page size is not 16";
+    else if (!(a.scale > 0.f)) r = "softmax scale is not positive";
+    else if (reinterpret_cast<uintptr_t>(a.q) % 16 || reinterpret_cast<uintptr_t>(a.out) % 16) r = "q/out are not 16-byte aligned";
+    else if (a.q_heads > 65535 || a.n_seqs > 65535) r = "more than 65535 heads or sequences";
+    if (why) *why = r;
+    return r == nullptr;
+}
+
+// Attention of each listed sequence's last query rows over the K/V the pool holds for it, on the tensor cores.
+ahpc_status launch_fa_paged_tc(const PagedPrefillLaunch& a) {
+    const char* why = nullptr;
+    if (!fa_paged_tc_supported(a, &why)) return fail(AHPC_UNSUPPORTED_OPERATION, "paged tensor-core kernel not applicable: %s", why);
+    CUtensorMap mq, mv;
+    // q as one [1, q_heads, total rows, D] view; v as [pages, kv_heads, 16, D]
+    const int64_t qs[4] = {a.total_q * a.q_heads * a.head_dim, a.head_stride, a.token_stride, 1};
+    const int64_t vs[4] = {a.page_elems, 16ll * a.head_dim, a.head_dim, 1};
+    AHPC_TRY(make_map(&mq, a.q, a.dtype, 1, a.q_heads, (int)a.total_q, a.head_dim, qs));
+    AHPC_TRY(make_map(&mv, a.v_data, a.dtype, a.num_pages, a.kv_heads, 16, a.head_dim, vs, 16));
+    TcParams p{};
+    p.out = a.out; p.lse = nullptr;
+    p.batch = 1; p.heads = a.q_heads; p.seq_q = a.max_q; p.seq_kv = 0;
+    p.os[0] = 0; p.os[1] = a.head_stride; p.os[2] = a.token_stride; p.os[3] = 1;
+    p.scale = a.scale;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.causal = a.causal;
+    p.n_pairs = (a.max_q + 2 * BM - 1) / (2 * BM);
+    p.kv_group = a.q_heads / a.kv_heads;
+    p.n_tiles = (a.max_q + BM - 1) / BM;
+    p.bh_group = 1;
+    p.paged.k_data = static_cast<const uint16_t*>(a.k_data);
+    p.paged.table = a.table;
+    p.paged.seqs = a.seqs_dev;
+    p.paged.page_elems = a.page_elems;
+    p.paged.max_pages = a.max_pages;
+    AHPC_TRY(error_word_for(a.device, &p.error_word));
+    const bool bf16 = a.dtype == AHPC_BF16;
+    if (a.head_dim == 128) return bf16 ? launch_paged<128, true>(a, mq, mv, p) : launch_paged<128, false>(a, mq, mv, p);
+    return bf16 ? launch_paged<64, true>(a, mq, mv, p) : launch_paged<64, false>(a, mq, mv, p);
+}
+
 ahpc_status launch_fa_tc(const FaLaunch& a, int variant) {
     const char* why = nullptr;
     if (!fa_tc_supported(a, &why)) return fail(AHPC_UNSUPPORTED_OPERATION, "tensor-core kernel not applicable: %s", why);
@@ -581,7 +712,7 @@ ahpc_status launch_fa_tc(const FaLaunch& a, int variant) {
     if (variant == AHPC_FA_KERNEL_TC) variant = a.dtype == AHPC_BF16 ? AHPC_FA_KERNEL_TC_DOUBLE_S : AHPC_FA_KERNEL_TC_TWO_TILE;
     // An explicit mask goes to the two-tile kernel: its rescaling softmax copes with rows whose first key tiles are masked
     // out entirely, where a reference maximum taken from key tile 0 would mean nothing.
-    if (a.mask) variant = AHPC_FA_KERNEL_TC_TWO_TILE;
+    if (a.mask || a.causal_offset) variant = AHPC_FA_KERNEL_TC_TWO_TILE;
     if (variant != AHPC_FA_KERNEL_TC_DOUBLE_S || tiles > REDO_RING_ENTRIES || tiles > 2147483647ll)
         return launch_two_tile(a, nullptr, nullptr);
     // double-buffered-score kernel, then the two-tile kernel over the tiles it flagged (normally none)

@@ -40,12 +40,13 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     }
 }
 
-// Key tiles the 128-row query tile starting at row r0 needs.
-__device__ __forceinline__ int kv_tiles_for(int r0, int seq_q, int seq_kv, int causal) {
+// Key tiles the 128-row query tile starting at row r0 needs; query row r stands at position r + offset
+// for the causal rule.
+__device__ __forceinline__ int kv_tiles_for(int r0, int seq_q, int seq_kv, int causal, int offset = 0) {
     if (r0 >= seq_q) return 0;
     int n = (seq_kv + BN - 1) / BN;
     if (causal) {
-        const int last_row = min(r0 + BM, seq_q) - 1;
+        const int last_row = min(r0 + BM, seq_q) - 1 + offset;
         n = min(n, last_row / BN + 1);
     }
     return n;

@@ -278,16 +278,42 @@ void PagedAttention::forward_batch(const std::vector<size_t>& sequence_ids, cons
     std::lock_guard<std::mutex> lock(sequences_mutex_);
     const size_t H = current_params_.num_heads, D = current_params_.head_dimension;
     const DataType dt = query_shapes[0].data_type;
-    std::vector<int32_t> slots(n);
+    std::vector<int32_t> slots(n), tokens(n);
+    bool decode_only = true;
     for (size_t i = 0; i < n; ++i) {
         const Sequence* s = find(sequence_ids[i]);
         if (!s) throw AttentionException(AttentionError::INVALID_INPUT, "Sequence not found");
         slots[i] = s->slot;
         if (!query_data[i] || !output_data[i]) throw AttentionException(AttentionError::INVALID_INPUT, "Null tensor data pointer");
-        if (query_shapes[i].total_elements() != H * D || output_shapes[i].total_elements() != H * D)
-            throw AttentionException(AttentionError::INVALID_INPUT, "decode expects one query token per sequence: shape {1,1,H,D}");
+        const size_t elems = query_shapes[i].total_elements();
+        if (elems == 0 || elems % (H * D) != 0 || output_shapes[i].total_elements() != elems)
+            throw AttentionException(AttentionError::INVALID_INPUT, "queries and outputs must be {1,S,H,D} tensors of the configured heads");
+        tokens[i] = static_cast<int32_t>(elems / (H * D));
+        decode_only = decode_only && tokens[i] == 1;
         if (query_shapes[i].data_type != dt || output_shapes[i].data_type != dt)
             throw AttentionException(AttentionError::INVALID_INPUT, "all queries and outputs of a batch must share one data type");
+    }
+    if (!decode_only) {
+        // Several query tokens for some sequence: its last S tokens attend to what the pool holds for it
+        // (compute_paged_attention with a longer query, paged_attention.cpp:596-680); buffers are [H,S,D].
+        for (size_t i = 0; i < n; ++i) {
+            ahpc_prefill_args pa{};
+            pa.pool = pool_;
+            pa.seqs = &slots[i]; pa.n_query = &tokens[i]; pa.n_seqs = 1;
+            pa.q = query_data[i]; pa.out = output_data[i];
+            pa.qo_dtype = static_cast<int32_t>(dt);
+            pa.q_heads = static_cast<int32_t>(H);
+            pa.scale = current_params_.scale_factor;
+            pa.causal = current_params_.causal_mask ? 1 : 0;
+            pa.stream = stream_;
+            pa.head_major = 1;
+            check(ahpc_paged_prefill(&pa));
+        }
+        if (profiling_enabled_) {
+            check(ahpc_stream_synchronize(device_, stream_));
+            profiling_results_.emplace_back("forward_batch", std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
+        }
+        return;
     }
     const size_t row_bytes = H * D * dtype_bytes(dt);
     ahpc_decode_args a{};

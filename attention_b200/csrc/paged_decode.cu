@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(const DecodeP
         const size_t pbase = (size_t)page * p.page_elems + (size_t)(head / p.kv_group) * PAGE * D;
         uint4 kreg[KP], vreg[SPG];
 #pragma unroll
-        for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)(half * KP + j) * PAGE + slot) * 8);
+        for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)((slot >> 3) * PIECES + half * KP + j) * 8 + (slot & 7)) * 8);
 #pragma unroll
         for (int i = 0; i < SPG; ++i) vreg[i] = ld_stream(vbase + pbase + (size_t)(vgrp * SPG + i) * D + vcol * 8);
 
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_gqa_kernel(const Dec
         const size_t pbase = (size_t)page * p.page_elems + (size_t)kvh * PAGE * D;
         uint4 kreg[KP], vreg[SPG];
 #pragma unroll
-        for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)(half * KP + j) * PAGE + slot) * 8);
+        for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)((slot >> 3) * PIECES + half * KP + j) * 8 + (slot & 7)) * 8);
 #pragma unroll
         for (int i = 0; i < SPG; ++i) vreg[i] = ld_stream(vbase + pbase + (size_t)(vgrp * SPG + i) * D + vcol * 8);
 

@@ -1,10 +1,14 @@
 // Paged KV pool: what lives where.
 //
 // In HBM (written only by kernels of kv_pool.cu):
-//   k_data   [num_pages][heads][head_dim/VEC][page_size][VEC]   VEC = 16 bytes / sizeof(element)
-//            keys, "slot-interleaved": the 16-byte pieces of one key are page_size*16 bytes apart,
-//            so that 16 consecutive lanes reading piece j of 16 consecutive slots touch one
-//            contiguous 256-byte run and every lane ends up owning one whole key.
+//   k_data   [num_pages][heads][page_size/8][head_dim/VEC][8][VEC]   VEC = 16 bytes / sizeof(element)
+//            keys, "slot-interleaved" in groups of 8 slots: piece j (16 bytes) of the 8 keys of a group
+//            is one contiguous 128-byte run, the runs of a group follow each other by piece.  Lanes that
+//            read piece j of consecutive slots touch whole 128-byte lines and every lane ends up owning
+//            one whole key (decode); and a page's block for one head, copied to shared memory as it
+//            lies, is the unswizzled K-major operand form of tcgen05.mma: 8-key x 16-byte core
+//            matrices, 128 bytes apart along the head dimension, head_dim*16 bytes apart along the
+//            keys (prefill over pages).  A page size that is not a multiple of 8 forms one group.
 //   v_data   [num_pages][heads][page_size][head_dim]
 //            values, row per slot: a lane owns 16 bytes of the head dimension of every slot.
 //   table    int32 [max_seqs][max_pages]   block table, -1 = no page
@@ -59,7 +63,10 @@ enum PoolCtrl { CTRL_HEAD = 0, CTRL_COUNT = 1, CTRL_ERROR = 2 };
 __host__ __device__ inline size_t k_piece_offset(size_t page_elems, int heads, int page_size, int head_dim, int vec,
                                                  int page, int head, int slot, int piece) {
     (void)heads;
-    return (size_t)page * page_elems + (size_t)head * page_size * head_dim + ((size_t)piece * page_size + slot) * vec;
+    const int group = page_size % 8 == 0 ? 8 : page_size;      // slots per group
+    const int pieces = head_dim / vec;
+    return (size_t)page * page_elems + (size_t)head * page_size * head_dim +
+           (((size_t)(slot / group) * pieces + piece) * group + slot % group) * vec;
 }
 // Element offset of value row `slot` of (page, head).
 __host__ __device__ inline size_t v_row_offset(size_t page_elems, int page_size, int head_dim, int page, int head, int slot) {

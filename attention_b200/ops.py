@@ -220,3 +220,22 @@ class KVPool:
         fn = abi.lib().ahpc_paged_decode_static if no_alloc else abi.lib().ahpc_paged_decode
         abi.check(fn(C.byref(a)))
         return out
+
+    def prefill(self, seqs, n_query, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, causal=True, head_major=False):
+        """The last n_query[i] tokens of each listed sequence (already appended) attend to what the pool holds for
+        it.  q: [sum(n_query), q_heads, head_dim], the sequences' query tokens concatenated; returns out alike.
+        head_major=True (one sequence): q and out are [q_heads, n_query, head_dim]."""
+        seqs, n_query = _i32(seqs), _i32(n_query)
+        assert seqs.size == n_query.size
+        tok, hd = (1, 0) if head_major else (0, 1)
+        assert q.is_contiguous() and q.dim() == 3 and q.shape[tok] == int(n_query.sum()) and q.shape[2] == self.head_dim
+        assert q.shape[hd] % self.heads == 0
+        if out is None:
+            out = torch.empty_like(q)
+        assert out.is_contiguous() and out.shape == q.shape and out.dtype == q.dtype
+        a = abi.PrefillArgs()
+        a.pool, a.seqs, a.n_query, a.n_seqs = self._p, _pi32(seqs), _pi32(n_query), seqs.size
+        a.q, a.out, a.qo_dtype, a.q_heads = q.data_ptr(), out.data_ptr(), _dtype_code(q), q.shape[hd]
+        a.scale, a.causal, a.stream, a.head_major = float(scale), int(bool(causal)), self._stream(), int(bool(head_major))
+        abi.check(abi.lib().ahpc_paged_prefill(C.byref(a)))
+        return out

@@ -288,6 +288,37 @@ AHPC_API ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* args);
 AHPC_API size_t ahpc_paged_decode_static_capacity(void);
 
 /* ------------------------------------------------------------------------------------------
+ * PagedAttention prefill over pages
+ * Several query tokens per sequence against the K/V the pool already holds for it: the last
+ * n_query[i] tokens of sequence seqs[i] (append them first) attend to all of the sequence's
+ * tokens, or - causal - to the tokens up to their own position.  This is what a chunked prefill
+ * or a prefill behind a shared prefix (ahpc_pool_seq_fork) needs.  Replaces the multi-token
+ * case of PagedAttention::forward / forward_batch (paged_attention.cpp:132-174, 496-547,
+ * 596-680), which gathers the pages into contiguous buffers first; here the tensor-core kernel
+ * reads the pages in place (FP16 / BF16 pools with page size 16 and head_dim 64 or 128 whose
+ * type is also that of q and out; other pools go through ahpc_pool_gather and the dense kernels).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct ahpc_prefill_args {
+    ahpc_pool* pool;
+    const int32_t* seqs;      /* host int32[n_seqs]: sequence slots                               */
+    const int32_t* n_query;   /* host int32[n_seqs]: query tokens per sequence, <= its length     */
+    int32_t n_seqs;
+    const void* q;            /* [sum(n_query), q_heads, head_dim] in qo_dtype, the sequences'
+                                 query tokens concatenated in list order                        */
+    void* out;                /* same shape and type                                              */
+    int32_t qo_dtype;
+    int32_t q_heads;          /* 0 = the pool's heads; else a multiple of them (grouped-query)    */
+    float scale;              /* 0 = 1/sqrt(head_dim)                                             */
+    int32_t causal;           /* non-zero: query token at position p sees keys 0..p only          */
+    void* stream;
+    int32_t head_major;       /* non-zero (n_seqs must be 1): q and out are [q_heads, n_query, head_dim],
+                                 the memory order of the reference's {1,S,H,D} tensors
+                                 (tests/test_flash_attention.cpp:46)                              */
+} ahpc_prefill_args;
+
+AHPC_API ahpc_status ahpc_paged_prefill(const ahpc_prefill_args* args);
+
+/* ------------------------------------------------------------------------------------------
  * Multi-GPU partitioning (host arithmetic only; no communication)
  * The (batch, head) pairs of a FlashAttention call, or the heads of a decode pool, are split
  * into `world` contiguous ranges, the first (units % world) ranges one unit longer.  The

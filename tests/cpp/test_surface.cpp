@@ -261,6 +261,22 @@ static void test_paged_attention() {
     for (int i = 0; i < 2; ++i)
         for (size_t e = 0; e < H * D; ++e) CHECK(std::fabs(o[i][e] - want[i * H * D + e]) <= 1e-3f);
 
+    {   // several query tokens for one sequence: b's last 30 tokens against all 100 held in pages ([H,S,D] buffers)
+        const size_t S = 30;
+        auto mq = random_data(H * S * D);
+        std::vector<float> mo(H * S * D), want_m(H * S * D), kd(H * lens[1] * D), vd(H * lens[1] * D);
+        for (size_t tok = 0; tok < lens[1]; ++tok)
+            for (size_t h = 0; h < H; ++h) {
+                std::memcpy(&kd[(h * lens[1] + tok) * D], &K[1][(tok * H + h) * D], D * 4);
+                std::memcpy(&vd[(h * lens[1] + tok) * D], &V[1][(tok * H + h) * D], D * 4);
+            }
+        TensorShape many({1, S, H, D}, DataType::FLOAT32);
+        paged->forward_batch({b}, {many}, {mq.data()}, {many}, {mo.data()});
+        const int64_t sq[4] = {int64_t(H * S * D), int64_t(S * D), int64_t(D), 1}, sk[4] = {int64_t(H * lens[1] * D), int64_t(lens[1] * D), int64_t(D), 1};
+        oracle_attention_fwd(mq.data(), kd.data(), vd.data(), want_m.data(), nullptr, 1, H, S, lens[1], D, sq, sk, sk, sq, 1.0f / std::sqrt(float(D)), 0, nullptr);
+        CHECK(max_abs_diff(mo, want_m) <= 1e-3f);
+    }
+
     CHECK_THROWS(paged->forward_batch({a, b}, {one}, {q[0].data()}, {one}, {o[0].data()}), AttentionError::INVALID_INPUT);   // sizes mismatch
     CHECK_THROWS(paged->forward_batch({size_t(99)}, {one}, {q[0].data()}, {one}, {o[0].data()}), AttentionError::INVALID_INPUT);
 

@@ -1,0 +1,141 @@
+"""GPU parity of the prefill over pages (several query tokens per sequence against the K/V the pool
+holds) against the CPU oracle's dense attention on the same tokens, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from attention_b200 import abi
+from oracle import cpu_oracle as o
+from tests import gpu_util as u
+from tests.test_paged_gpu import DEV, Mirror
+
+pytestmark = pytest.mark.gpu
+
+
+def sequence_kv(m: Mirror, seq: int, group: int = 1):
+    """What the pool holds for `seq`, as the oracle's [1, H, len, D] tensors."""
+    n = m.model.seq_len(seq)
+    bt = m.model.block_table(seq)
+    k = np.stack([m.kc[bt[t // m.ps], t % m.ps] for t in range(n)])       # [len, H, D]
+    v = np.stack([m.vc[bt[t // m.ps], t % m.ps] for t in range(n)])
+    k, v = (np.repeat(x, group, axis=1) for x in (k, v))
+    return np.ascontiguousarray(k.transpose(1, 0, 2))[None], np.ascontiguousarray(v.transpose(1, 0, 2))[None]
+
+
+def prefill_check(m: Mirror, seqs, n_query, *, causal=True, group=1, qo_dtype=None, host=False, scale=0.0):
+    qo_dtype = qo_dtype or m.dtype
+    total = int(sum(n_query))
+    q = o.round_to(m.rng.standard_normal((total, m.H * group, m.D)).astype(np.float32), qo_dtype)
+    tq = u.payload_to_torch(q, qo_dtype)
+    if not host:
+        tq = tq.to(DEV)
+    out = u.torch_to_f32(m.pool.prefill(seqs, n_query, tq, causal=causal, scale=scale))
+    qf = o.widen(q, qo_dtype)
+    sc = scale if scale else 1.0 / np.sqrt(m.D)
+    row = 0
+    for s, n in zip(seqs, n_query):
+        if n == 0:
+            continue
+        k, v = sequence_kv(m, s, group)
+        length = k.shape[2]
+        qs = qf[row:row + n].transpose(1, 0, 2)[None]                     # [1, Hq, n, D]
+        if causal:
+            # the queries are the sequence's last n tokens: run the oracle with them at their positions
+            full = np.zeros((1, m.H * group, length, m.D), np.float32)
+            full[:, :, length - n:] = qs
+            want = o.attention_fwd(full, k, v, sc, causal=True)[:, :, length - n:]
+        else:
+            want = o.attention_fwd(np.ascontiguousarray(qs), k, v, sc, causal=False)
+        got = out[row:row + n].transpose(1, 0, 2)[None]
+        u.assert_close(got, want, qo_dtype, f"prefill seq={s} len={length} n_query={n} causal={causal}")
+        row += n
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("D", [64, 128])
+def test_prefill_over_pages_ragged_batch(dtype, D):
+    m = Mirror(num_pages=120, heads=2, head_dim=D, dtype=dtype, max_seqs=8, max_pages=40, seed=11)
+    lens = [5, 16, 130, 300, 257, 512]
+    seqs = [m.create() for _ in lens]
+    m.append(seqs, lens)
+    m.check_tables()
+    prefill_check(m, seqs, [5, 3, 130, 44, 257, 1])                       # whole prompts, chunks, one token
+    prefill_check(m, seqs[2:5], [128, 300, 129], causal=False)
+    prefill_check(m, [seqs[3]], [0])                                       # nothing to do
+
+
+@pytest.mark.parametrize("group", [2, 4])
+def test_prefill_grouped_query_attention(group):
+    m = Mirror(num_pages=80, heads=2, head_dim=128, dtype="bf16", max_seqs=4, max_pages=40, seed=12)
+    a, b = m.create(), m.create()
+    m.append([a, b], [333, 90])
+    prefill_check(m, [a, b], [200, 90], group=group)
+
+
+def test_prefill_long_sequence_many_tiles():
+    m = Mirror(num_pages=140, heads=1, head_dim=128, dtype="bf16", max_seqs=2, max_pages=140, seed=13)
+    a = m.create()
+    m.append([a], [2100])
+    prefill_check(m, [a], [1000])                                          # four pairs of query tiles, 17 key tiles
+    prefill_check(m, [a], [2100], causal=False)
+
+
+def test_prefill_behind_a_shared_prefix():
+    m = Mirror(num_pages=60, heads=2, head_dim=64, dtype="f16", max_seqs=4, max_pages=20, seed=14)
+    a = m.create()
+    m.append([a], [100])
+    b = m.pool.seq_fork(a, 70)
+    bm, frm, to = m.model.fork(a, 70)
+    assert b == bm
+    m.kc[to, : 70 % 16] = m.kc[frm, : 70 % 16]                           # the fork owns a copy of the partial page
+    m.vc[to, : 70 % 16] = m.vc[frm, : 70 % 16]
+    m.append([b], [45])                                                    # the new suffix
+    m.check_tables()
+    prefill_check(m, [b, a], [45, 100])
+
+
+@pytest.mark.parametrize("cfg", [dict(dtype="f32", page_size=16, D=64), dict(dtype="f16", page_size=8, D=128),
+                                 dict(dtype="bf16", page_size=16, D=96)])
+def test_prefill_general_path(cfg):
+    """Pools the page-walking kernel does not take go through a gather and the dense kernels."""
+    m = Mirror(num_pages=64, heads=2, head_dim=cfg["D"], dtype=cfg["dtype"], page_size=cfg["page_size"], max_seqs=4, max_pages=40, seed=15)
+    a, b = m.create(), m.create()
+    m.append([a, b], [150, 37])
+    prefill_check(m, [a, b], [60, 37])
+    prefill_check(m, [a], [150], causal=False)
+
+
+def test_prefill_query_type_other_than_the_pool_and_host_tensors():
+    m = Mirror(num_pages=40, heads=2, head_dim=64, dtype="f16", max_seqs=4, max_pages=20, seed=16)
+    a = m.create()
+    m.append([a], [140])
+    prefill_check(m, [a], [100], qo_dtype="f32", scale=0.2)
+    prefill_check(m, [a], [140], host=True)
+
+
+def test_prefill_head_major_buffers():
+    """One sequence with q and out as [heads, tokens, D], the memory order of the reference's {1,S,H,D} tensors."""
+    m = Mirror(num_pages=40, heads=2, head_dim=128, dtype="bf16", max_seqs=2, max_pages=30, seed=18)
+    a = m.create()
+    m.append([a], [400])
+    n = 270
+    q = o.round_to(m.rng.standard_normal((2, n, 128)).astype(np.float32), "bf16")          # [H, n, D]
+    out = u.torch_to_f32(m.pool.prefill([a], [n], u.payload_to_torch(q, "bf16").to(DEV), head_major=True))
+    k, v = sequence_kv(m, a)
+    full = np.zeros((1, 2, 400, 128), np.float32)
+    full[0, :, 400 - n:] = o.widen(q, "bf16")
+    want = o.attention_fwd(full, k, v, 1.0 / np.sqrt(128), causal=True)[0, :, 400 - n:]
+    u.assert_close(out, want, "bf16", "head-major prefill")
+
+
+def test_prefill_rejects_bad_arguments():
+    m = Mirror(num_pages=20, heads=2, head_dim=64, dtype="f16", max_seqs=4, max_pages=10, seed=17)
+    a = m.create()
+    m.append([a], [20])
+    q = torch.zeros((21, 2, 64), dtype=torch.float16, device=DEV)
+    with pytest.raises(abi.AhpcError) as e:
+        m.pool.prefill([a], [21], q)                                       # more query tokens than the sequence holds
+    assert e.value.status == 2
+    with pytest.raises(abi.AhpcError) as e:
+        m.pool.prefill([3], [1], q[:1])                                    # no such sequence
+    assert e.value.status == 1
