@@ -31,7 +31,7 @@ EXPORTED_SYMBOLS = [
     "ahpc_pool_seq_len", "ahpc_pool_seq_pages", "ahpc_pool_free_pages", "ahpc_pool_page_bytes",
     "ahpc_pool_live_seqs", "ahpc_pool_read_block_table", "ahpc_pool_read_seq_lens",
     "ahpc_pool_read_refcounts", "ahpc_pool_read_free_ring", "ahpc_pool_read_error_flag",
-    "ahpc_paged_decode", "ahpc_paged_decode_scratch_bytes", "ahpc_paged_decode_static",
+    "ahpc_paged_decode", "ahpc_paged_decode_step", "ahpc_paged_decode_scratch_bytes", "ahpc_paged_decode_static",
     "ahpc_paged_decode_static_capacity", "ahpc_paged_prefill", "ahpc_shard_range",
 ]
 
@@ -139,6 +139,7 @@ def lib() -> C.CDLL:
     L.ahpc_pool_read_free_ring.argtypes = [vp, pi32, i32, C.POINTER(i64), vp]
     L.ahpc_pool_read_error_flag.argtypes = [vp, pi32, vp]
     L.ahpc_paged_decode.argtypes = [C.POINTER(DecodeArgs)]
+    L.ahpc_paged_decode_step.argtypes = [C.POINTER(DecodeArgs), vp, vp, i32]
     L.ahpc_paged_decode_static.argtypes = [C.POINTER(DecodeArgs)]
     L.ahpc_paged_decode_static_capacity.restype = C.c_size_t
     L.ahpc_paged_decode_scratch_bytes.argtypes = [vp, i32, i32, i32]

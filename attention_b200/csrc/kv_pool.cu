@@ -486,9 +486,17 @@ ahpc_status ahpc_pool_append(ahpc_pool* p, const int32_t* seqs, const int32_t* n
     if (n <= 0) return AHPC_SUCCESS;
     if (!dtype_valid(kv_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_append: unknown kv dtype %d", kv_dtype);
     std::lock_guard<std::mutex> lock(p->mu);
-    if (n > p->cfg.max_seqs) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_append: %d sequences listed, pool holds %d", n, p->cfg.max_seqs);
-    cudaStream_t st = (cudaStream_t)stream;
     ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
+    return pool_append_locked(p, seqs, n_tokens, n, k, v, kv_dtype, (cudaStream_t)stream, true);
+}
+
+}  // extern "C"
+
+// The body of ahpc_pool_append; the caller holds the pool's mutex and has made its device current.  With
+// scatter = false only the pages are allotted and the lengths moved on: the caller's next kernel writes the tokens.
+ahpc_status ahpc::pool_append_locked(ahpc_pool* p, const int32_t* seqs, const int32_t* n_tokens, int n, const void* k, const void* v,
+                                     int kv_dtype, cudaStream_t st, bool scatter) {
+    if (n > p->cfg.max_seqs) return fail(AHPC_INVALID_PARAMETERS, "ahpc_pool_append: %d sequences listed, pool holds %d", n, p->cfg.max_seqs);
 
     std::vector<int32_t> host_args(3 * (size_t)n);
     std::vector<uint8_t> listed(p->cfg.max_seqs, 0);
@@ -520,7 +528,7 @@ ahpc_status ahpc_pool_append(ahpc_pool* p, const int32_t* seqs, const int32_t* n
     }
     if (total_tokens == 0) return AHPC_SUCCESS;
 
-    const bool host_kv = is_host_pointer(k) || is_host_pointer(v);
+    const bool host_kv = scatter && (is_host_pointer(k) || is_host_pointer(v));
     const void *dk = k, *dv = v;
     if (host_kv) {
         const size_t bytes = (size_t)total_tokens * p->cfg.heads * p->cfg.head_dim * dtype_size(kv_dtype);
@@ -535,8 +543,9 @@ ahpc_status ahpc_pool_append(ahpc_pool* p, const int32_t* seqs, const int32_t* n
     pool_append_alloc_kernel<<<1, ALLOC_THREADS, 0, st>>>(p->call_args, n, p->table, p->seq_len, p->seq_pages, p->refcount, p->ring, p->ctrl,
                                                           p->cfg.num_pages, p->cfg.page_size, p->cfg.max_pages_per_seq);
     AHPC_CUDA_OK(cudaGetLastError());
-    ahpc_status s;
-    if (p->cfg.dtype == AHPC_F32) s = scatter_dispatch<float>(p, dk, dv, kv_dtype, n, max_tokens, st);
+    ahpc_status s = AHPC_SUCCESS;
+    if (!scatter) {}
+    else if (p->cfg.dtype == AHPC_F32) s = scatter_dispatch<float>(p, dk, dv, kv_dtype, n, max_tokens, st);
     else if (p->cfg.dtype == AHPC_F16) s = scatter_dispatch<__half>(p, dk, dv, kv_dtype, n, max_tokens, st);
     else s = scatter_dispatch<__nv_bfloat16>(p, dk, dv, kv_dtype, n, max_tokens, st);
     AHPC_TRY(s);
@@ -551,6 +560,8 @@ ahpc_status ahpc_pool_append(ahpc_pool* p, const int32_t* seqs, const int32_t* n
     if (host_kv) AHPC_CUDA_OK(cudaStreamSynchronize(st));
     return AHPC_SUCCESS;
 }
+
+extern "C" {
 
 ahpc_status ahpc_pool_gather(ahpc_pool* p, int32_t seq, int32_t start, int32_t n, void* k_out, void* v_out, int32_t out_dtype, void* stream) {
     if (!p || !k_out || !v_out) return fail(AHPC_INVALID_INPUT, "ahpc_pool_gather: NULL argument");

@@ -19,6 +19,7 @@
 
 #include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "pool.cuh"
 
@@ -43,6 +44,11 @@ struct DecodeParams {
     int kv_heads, kv_group;    // heads of the pool; query head h reads key/value head h / kv_group
     size_t page_elems;
     float scale_log2;          // softmax scale * log2(e)
+    // Decode step with the append folded in (fast kernels only): the token every listed sequence gained just before this
+    // launch - its pages are allotted and seq_len counts it, but nobody wrote it - as [n_seqs][kv_heads][head_dim] in the
+    // pool's type.  The kernels read that token from here instead of the pool, and one CTA per key/value head stores it.
+    const void* new_k;
+    const void* new_v;
 };
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
@@ -66,6 +72,33 @@ template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
     float2 a = Pair<T>::unpack(u.x), b = Pair<T>::unpack(u.y), c = Pair<T>::unpack(u.z), d = Pair<T>::unpack(u.w);
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+// The page a warp of a fast kernel has just loaded holds the slot of the token this step appends: the lanes that own a
+// piece of that key, or of that value row, take it from the call's new_k / new_v instead (what they read from the pool was
+// never written), and in the CTA that is the writer for this key/value head they also store it where it belongs.
+template <typename T, int D>
+__device__ __forceinline__ void take_new_token(const DecodeParams& p, uint4 (&kreg)[D / 16], uint4 (&vreg)[16 / (32 / (D / 8))], int si, int kvh,
+                                               bool writer, size_t pbase, int last_slot, int lane) {
+    constexpr int PAGE = 16, PIECES = D / 8, KP = PIECES / 2, LPR = PIECES, SPG = PAGE / (32 / LPR);
+    const int slot = lane & 15, half = lane >> 4, vcol = lane % LPR, vgrp = lane / LPR;
+    const T* nk = static_cast<const T*>(p.new_k) + ((size_t)si * p.kv_heads + kvh) * D;
+    const T* nv = static_cast<const T*>(p.new_v) + ((size_t)si * p.kv_heads + kvh) * D;
+    T* kpool = static_cast<T*>(const_cast<void*>(p.k_data));
+    T* vpool = static_cast<T*>(const_cast<void*>(p.v_data));
+    if (slot == last_slot) {
+#pragma unroll
+        for (int j = 0; j < KP; ++j) {
+            kreg[j] = *reinterpret_cast<const uint4*>(nk + (half * KP + j) * 8);
+            if (writer) *reinterpret_cast<uint4*>(kpool + pbase + ((size_t)((slot >> 3) * PIECES + half * KP + j) * 8 + (slot & 7)) * 8) = kreg[j];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < SPG; ++i)
+        if (vgrp * SPG + i == last_slot) {
+            vreg[i] = *reinterpret_cast<const uint4*>(nv + vcol * 8);
+            if (writer) *reinterpret_cast<uint4*>(vpool + pbase + (size_t)(vgrp * SPG + i) * D + vcol * 8) = vreg[i];
+        }
 }
 
 // Fast path: 16-bit pool, page size 16, head_dim D in {64, 128}.
@@ -105,6 +138,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(const DecodeP
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 
+    const int last_col = (len - 1) / PAGE, last_slot = (len - 1) % PAGE;     // where a folded-in append puts its token
     for (int pi = warp; pi < n_pages; pi += DEC_WARPS) {
         const int page = row[page0 + pi];
         if (page < 0) break;                                  // table shorter than the length says: stop (cuda_kernels.cu:419-420)
@@ -114,6 +148,8 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(const DecodeP
         for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)((slot >> 3) * PIECES + half * KP + j) * 8 + (slot & 7)) * 8);
 #pragma unroll
         for (int i = 0; i < SPG; ++i) vreg[i] = ld_stream(vbase + pbase + (size_t)(vgrp * SPG + i) * D + vcol * 8);
+        if (p.new_k && page0 + pi == last_col)
+            take_new_token<T, D>(p, kreg, vreg, si, head / p.kv_group, head % p.kv_group == 0, pbase, last_slot, lane);
 
         float s = 0.f;
 #pragma unroll
@@ -229,6 +265,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_gqa_kernel(const Dec
         for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
     }
 
+    const int last_col = (len - 1) / PAGE, last_slot = (len - 1) % PAGE;     // where a folded-in append puts its token
     for (int pi = warp; pi < n_pages; pi += DEC_WARPS) {
         const int page = row[page0 + pi];
         if (page < 0) break;
@@ -238,6 +275,8 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_gqa_kernel(const Dec
         for (int j = 0; j < KP; ++j) kreg[j] = ld_stream(kbase + pbase + ((size_t)((slot >> 3) * PIECES + half * KP + j) * 8 + (slot & 7)) * 8);
 #pragma unroll
         for (int i = 0; i < SPG; ++i) vreg[i] = ld_stream(vbase + pbase + (size_t)(vgrp * SPG + i) * D + vcol * 8);
+        if (p.new_k && page0 + pi == last_col)
+            take_new_token<T, D>(p, kreg, vreg, si, kvh, qh0 % p.kv_group == 0, pbase, last_slot, lane);
 
         float s[G];
 #pragma unroll
@@ -566,17 +605,9 @@ size_t ahpc_paged_decode_scratch_bytes(const ahpc_pool* p, int32_t n_seqs, int32
     return scratch_layout(n_seqs, max_chunks, p->cfg.heads, p->cfg.head_dim).total;
 }
 
-ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
-    if (!a || !a->pool) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode: NULL argument");
+// The decode proper; the caller holds the pool's mutex and has made its device current.  new_k / new_v: see DecodeParams.
+static ahpc_status decode_locked(const ahpc_decode_args* a, int q_heads, const void* new_k, const void* new_v) {
     ahpc_pool* p = a->pool;
-    if (a->n_seqs <= 0) return AHPC_SUCCESS;
-    if (!a->seqs || !a->q || !a->out) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode: seqs, q and out must not be NULL");
-    if (!dtype_valid(a->qo_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: unknown dtype %d", a->qo_dtype);
-    if (a->n_seqs > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_decode: at most 65535 sequences per call");
-    int q_heads = 0;
-    AHPC_TRY(query_heads(a, "ahpc_paged_decode", &q_heads));
-    std::lock_guard<std::mutex> lock(p->mu);
-    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     cudaStream_t st = (cudaStream_t)a->stream;
     int max_len = 0;
     for (int i = 0; i < a->n_seqs; ++i) {
@@ -626,6 +657,7 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
     dp.page_elems = p->page_elems;
     const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);
     dp.scale_log2 = scale * LOG2E;
+    dp.new_k = new_k; dp.new_v = new_v;
 
     ahpc_status s;
     if (p->cfg.dtype == AHPC_F32) s = launch_decode_q<float>(p, dp, a->qo_dtype, st);
@@ -635,6 +667,43 @@ ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
     if (host_o) AHPC_CUDA_OK(cudaMemcpyAsync(a->out, dout, qo_bytes, cudaMemcpyDeviceToHost, st));
     if (host_q || host_o) AHPC_CUDA_OK(cudaStreamSynchronize(st));
     return AHPC_SUCCESS;
+}
+
+static ahpc_status decode_args_ok(const ahpc_decode_args* a, const char* who, int* q_heads) {
+    if (!a || !a->pool) return fail(AHPC_INVALID_INPUT, "%s: NULL argument", who);
+    if (a->n_seqs <= 0) return AHPC_SUCCESS;
+    if (!a->seqs || !a->q || !a->out) return fail(AHPC_INVALID_INPUT, "%s: seqs, q and out must not be NULL", who);
+    if (!dtype_valid(a->qo_dtype)) return fail(AHPC_INVALID_PARAMETERS, "%s: unknown dtype %d", who, a->qo_dtype);
+    if (a->n_seqs > 65535) return fail(AHPC_UNSUPPORTED_OPERATION, "%s: at most 65535 sequences per call", who);
+    return query_heads(a, who, q_heads);
+}
+
+ahpc_status ahpc_paged_decode(const ahpc_decode_args* a) {
+    int q_heads = 0;
+    AHPC_TRY(decode_args_ok(a, "ahpc_paged_decode", &q_heads));
+    if (a->n_seqs <= 0) return AHPC_SUCCESS;
+    ahpc_pool* p = a->pool;
+    std::lock_guard<std::mutex> lock(p->mu);
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
+    return decode_locked(a, q_heads, nullptr, nullptr);
+}
+
+ahpc_status ahpc_paged_decode_step(const ahpc_decode_args* a, const void* k_new, const void* v_new, int32_t kv_dtype) {
+    int q_heads = 0;
+    AHPC_TRY(decode_args_ok(a, "ahpc_paged_decode_step", &q_heads));
+    if (a->n_seqs <= 0) return AHPC_SUCCESS;
+    if (!k_new || !v_new) return fail(AHPC_INVALID_INPUT, "ahpc_paged_decode_step: k_new and v_new must not be NULL");
+    if (!dtype_valid(kv_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode_step: unknown kv dtype %d", kv_dtype);
+    ahpc_pool* p = a->pool;
+    std::lock_guard<std::mutex> lock(p->mu);
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
+    // The fast kernels can take the new token straight from the caller's tensors and store it on their way; everything
+    // else (other pool layouts, another element type, host tensors) appends first and decodes afterwards.
+    const bool fold = fast_path(p) && kv_dtype == p->cfg.dtype && !is_host_pointer(k_new) && !is_host_pointer(v_new) &&
+                      reinterpret_cast<uintptr_t>(k_new) % 16 == 0 && reinterpret_cast<uintptr_t>(v_new) % 16 == 0;
+    const std::vector<int32_t> ones((size_t)a->n_seqs, 1);
+    AHPC_TRY(pool_append_locked(p, a->seqs, ones.data(), a->n_seqs, k_new, v_new, kv_dtype, (cudaStream_t)a->stream, !fold));
+    return decode_locked(a, q_heads, fold ? k_new : nullptr, fold ? v_new : nullptr);
 }
 
 size_t ahpc_paged_decode_static_capacity(void) { return STATIC_SCRATCH_BYTES; }
@@ -690,6 +759,7 @@ ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* a) {
     dp.page_elems = p->page_elems;
     const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);
     dp.scale_log2 = scale * LOG2E;
+    dp.new_k = dp.new_v = nullptr;
     if (p->cfg.dtype == AHPC_F32) return launch_decode_q<float>(p, dp, a->qo_dtype, st);
     if (p->cfg.dtype == AHPC_F16) return launch_decode_q<__half>(p, dp, a->qo_dtype, st);
     return launch_decode_q<__nv_bfloat16>(p, dp, a->qo_dtype, st);

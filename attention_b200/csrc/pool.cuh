@@ -68,6 +68,11 @@ __host__ __device__ inline size_t k_piece_offset(size_t page_elems, int heads, i
     return (size_t)page * page_elems + (size_t)head * page_size * head_dim +
            (((size_t)(slot / group) * pieces + piece) * group + slot % group) * vec;
 }
+// ahpc_pool_append for a caller that holds the pool's mutex and has made its device current (kv_pool.cu).
+// scatter = false: pages are allotted and lengths moved on, the tokens themselves are left to the caller's kernel.
+ahpc_status pool_append_locked(ahpc_pool* p, const int32_t* seqs, const int32_t* n_tokens, int n, const void* k, const void* v,
+                               int kv_dtype, cudaStream_t st, bool scatter);
+
 // Element offset of value row `slot` of (page, head).
 __host__ __device__ inline size_t v_row_offset(size_t page_elems, int page_size, int head_dim, int page, int head, int slot) {
     return (size_t)page * page_elems + ((size_t)head * page_size + slot) * head_dim;

@@ -202,10 +202,12 @@ class KVPool:
         abi.check(abi.lib().ahpc_pool_read_error_flag(self._p, C.byref(f), self._stream()))
         return f.value
 
-    def decode(self, seqs, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, split_tokens=0, no_alloc=False):
+    def decode(self, seqs, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, split_tokens=0, no_alloc=False,
+               k_new: torch.Tensor | None = None, v_new: torch.Tensor | None = None):
         """q: [n_seqs, q_heads, head_dim], q_heads a multiple of the pool's heads (grouped-query attention when
         larger); returns out of the same shape and dtype.  no_alloc=True goes through ahpc_paged_decode_static
-        (fixed built-in scratch, device tensors only)."""
+        (fixed built-in scratch, device tensors only).  k_new, v_new ([n_seqs, heads, head_dim]): one token
+        appended to every listed sequence before it is attended to (ahpc_paged_decode_step)."""
         seqs = _i32(seqs)
         assert q.is_contiguous() and q.dim() == 3 and q.shape[0] == seqs.size and q.shape[2] == self.head_dim
         assert q.shape[1] % self.heads == 0
@@ -217,6 +219,11 @@ class KVPool:
         a.q, a.out, a.qo_dtype = q.data_ptr(), out.data_ptr(), _dtype_code(q)
         a.scale, a.split_tokens, a.stream = float(scale), int(split_tokens), self._stream()
         a.q_heads = q.shape[1]
+        if k_new is not None:
+            assert not no_alloc and v_new is not None and k_new.is_contiguous() and v_new.is_contiguous() and k_new.dtype == v_new.dtype
+            assert tuple(k_new.shape) == (seqs.size, self.heads, self.head_dim) == tuple(v_new.shape)
+            abi.check(abi.lib().ahpc_paged_decode_step(C.byref(a), k_new.data_ptr(), v_new.data_ptr(), _dtype_code(k_new)))
+            return out
         fn = abi.lib().ahpc_paged_decode_static if no_alloc else abi.lib().ahpc_paged_decode
         abi.check(fn(C.byref(a)))
         return out

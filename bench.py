@@ -7,7 +7,8 @@ Prints ONE JSON line.  The headline workload is BASELINE configuration 2 (FlashA
 BF16, causal, B=4 S=4096 H=32 D=128, N(0,1)*0.5, synthetic): metric = forward TFLOPS, a step = one
 forward over one batch.  The same line carries the PagedAttention decode of configuration 3 (FP16,
 batch 64, H=32 D=128, page 16, context ~ U[512, 8192]) under "paged_decode": HBM GB/s, tokens/s and
-its own roofline / end-to-end / CPU-baseline figures.
+its own roofline / end-to-end / CPU-baseline figures, and under "paged_prefill" the headline
+workload once more with K/V held in a paged pool (ahpc_paged_prefill reading the pages in place).
 
   value        kernel-only throughput, inputs resident in HBM, CUDA events, max over ranks
   e2e          the same metric through the C ABI with HOST (pinned) buffers: every step copies its
@@ -284,6 +285,42 @@ def bench_fa(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind):
     return res
 
 
+def bench_paged_prefill(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind):
+    """The FlashAttention workload once more with K/V held in a paged pool (pages dealt from a seeded permutation):
+    every sequence's tokens attend causally to the pages, read in place by ahpc_paged_prefill."""
+    from attention_b200 import ops, synth
+    q, k, v = make_fa_inputs(torch, cfg, rank)
+    dense = ops.flash_attention_forward(q, k, v, causal=cfg.causal)
+    ps = 16
+    pages = cfg.batch * ((cfg.seq + ps - 1) // ps) + 8
+    pool = ops.KVPool(num_pages=pages, heads=cfg.heads, head_dim=cfg.head_dim, dtype=q.dtype, page_size=ps, max_seqs=cfg.batch,
+                      max_pages_per_seq=(cfg.seq + ps - 1) // ps, device=torch.cuda.current_device(),
+                      free_order=synth.page_permutation(pages, cfg.seed + rank))
+    seqs = [pool.seq_create() for _ in range(cfg.batch)]
+    for b, s in enumerate(seqs):
+        pool.append([s], [cfg.seq], k[b].permute(1, 0, 2).contiguous(), v[b].permute(1, 0, 2).contiguous())
+    qt = q.permute(0, 2, 1, 3).reshape(cfg.batch * cfg.seq, cfg.heads, cfg.head_dim).contiguous()      # [tokens, H, D]
+    out = torch.empty_like(qt)
+    del k, v
+    counts = [cfg.seq] * cfg.batch
+
+    def step():
+        pool.prefill(seqs, counts, qt, out, causal=cfg.causal)
+
+    ms_per_step = timed_steps(torch, dist, step, args.steps, args.warmup) / args.steps
+    diff = (out.reshape(cfg.batch, cfg.seq, cfg.heads, cfg.head_dim).permute(0, 2, 1, 3).float() - dense.float()).abs().max().item()
+    tflops_rank = cfg.flops / (ms_per_step * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"]
+    res = {"metric": "paged_prefill_tflops", "unit": "TFLOPS", "value": tflops_rank * world, "ms_per_step": ms_per_step, "dtype": cfg.dtype,
+           "config": {"workload": f"{workload_name(cfg)}; K/V in a pool of {pages} pages of {ps} tokens, seeded page permutation"},
+           "max_abs_diff_vs_dense_kernel": diff,
+           "roofline": {"bound": "tensor", "achieved": tflops_rank, "peak": peak, "unit": "TFLOP/s", "frac": tflops_rank / peak,
+                        "traffic": None, "peak_source": peak_kind + " burst", "kernel": "fa_fwd_tc_kernel<PAGED>", "flops_per_launch": cfg.flops},
+           "gpu_launches": args.steps}
+    pool.close()
+    return res
+
+
 def build_decode_pool(torch, cfg, rank: int):
     """Pool filled with the configuration's sequences: pages dealt from the seeded permutation, prefixes
     shared by fork when the configuration asks for sharing."""
@@ -388,6 +425,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode section")
     ap.add_argument("--decode", choices=["c3", "c5"], default="c3",
                     help="paged-decode configuration: c3 (batch 64, U[512,8192]) or c5 (batch 256, logU[1024,32768], shared prefixes)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill-over-pages section")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--strong", action="store_true",
                     help="strong scaling: the heads of ONE configuration are split over the ranks (ahpc_shard_range) instead of "
@@ -437,6 +475,10 @@ def main():
 
     fa = bench_fa(torch, dist, cfg, args, rank, world, peaks, peak_kind)
     torch.cuda.empty_cache()
+    pre = None
+    if not args.no_prefill and not args.profile_small:
+        pre = bench_paged_prefill(torch, dist, cfg, args, rank, world, peaks, peak_kind)
+        torch.cuda.empty_cache()
     dec = None
     if not args.no_decode:
         dec = bench_decode(torch, dist, dec_cfg, args, rank, world, peaks, peak_kind)
@@ -456,6 +498,9 @@ def main():
         if not args.no_cpu_baseline:
             tflops, sample, _, threads = cpu_fa_baseline(cfg, budget_s=15.0)
             line["cpu_baseline"] = {"value": tflops, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample}
+        if pre is not None:
+            line["paged_prefill"] = pre
+            line["gpu_launches"] += pre["gpu_launches"]
         if dec is not None:
             if not args.no_cpu_baseline:
                 gbs, tps, sample, threads = cpu_decode_baseline(dec_cfg, budget_s=10.0)

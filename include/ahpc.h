@@ -252,6 +252,19 @@ typedef struct ahpc_decode_args {
 
 AHPC_API ahpc_status ahpc_paged_decode(const ahpc_decode_args* args);
 
+/* One step of a serving loop: every listed sequence first gains one token - k_new, v_new:
+ * [n_seqs, heads, head_dim] of the pool's heads in kv_dtype, as ahpc_pool_append takes them with
+ * one token per sequence; no sequence may be listed twice - and then its query attends to all its
+ * tokens, the new one included.  The result and the pool afterwards are those of ahpc_pool_append
+ * followed by ahpc_paged_decode.  On 16-bit pools with page size 16 and head_dim 64 or 128, device
+ * tensors of the pool's type, the decode kernel itself takes the new token from k_new / v_new and
+ * stores it into its page, so the step costs the page allotment and the decode launches only
+ * (append_kv_cache + forward_batch of the reference in one call, paged_attention.cpp:434-462,
+ * 496-547; update_kv_cache_kernel folded into paged_attention_kernel, cuda_kernels.cu:370-563).
+ * Fails like ahpc_pool_append, changing nothing, when pages or table columns run out. */
+AHPC_API ahpc_status ahpc_paged_decode_step(const ahpc_decode_args* args, const void* k_new, const void* v_new,
+                                            int32_t kv_dtype);
+
 /* Bytes of split-KV scratch (partial outputs and log-sum-exp) a decode of n_seqs sequences of
  * at most max_len tokens needs; the library keeps this buffer per pool and grows it on demand. */
 AHPC_API size_t ahpc_paged_decode_scratch_bytes(const ahpc_pool* pool, int32_t n_seqs, int32_t max_len,

@@ -91,6 +91,14 @@ def test_pool_config_validation(native_lib):
     assert native_lib.ahpc_pool_create(None, None) == 1
 
 
+def test_prefill_and_step_reject_null_arguments(native_lib):
+    assert native_lib.ahpc_paged_prefill(None) == 1
+    assert native_lib.ahpc_paged_prefill(C.byref(abi.PrefillArgs())) == 1          # no pool
+    assert native_lib.ahpc_paged_decode_step(None, None, None, 1) == 1
+    assert native_lib.ahpc_paged_decode_step(C.byref(abi.DecodeArgs()), None, None, 1) == 1
+    assert b"NULL" in native_lib.ahpc_last_error_string()
+
+
 def test_strides(native_lib):
     assert abi.fa_strides(abi.LAYOUT_BHSD, 2, 8, 512, 64) == (8 * 512 * 64, 512 * 64, 64, 1)
     assert abi.fa_strides(abi.LAYOUT_BSHD, 2, 8, 512, 64) == (512 * 8 * 64, 64, 8 * 64, 1)

@@ -82,6 +82,81 @@ class Mirror:
         return out
 
 
+def step_check(m: Mirror, seqs, *, group=1, kv_dtype=None, host=False, split=0):
+    """One decode step with the append folded in: every listed sequence gains a token, then decodes.  Checks the output
+    against the oracle on the mirrored caches, the block tables against the CPU model and the stored token by a gather."""
+    kv_dtype = kv_dtype or m.dtype
+    n = len(seqs)
+    k = o.round_to(o.widen(o.round_to(m.rng.standard_normal((n, m.H, m.D)).astype(np.float32), m.dtype), m.dtype), kv_dtype)
+    v = o.round_to(o.widen(o.round_to(m.rng.standard_normal((n, m.H, m.D)).astype(np.float32), m.dtype), m.dtype), kv_dtype)
+    for i, s in enumerate(seqs):
+        pos = m.model.seq_len(s)
+        assert m.model.append(s, 1) == 0
+        bt = m.model.block_table(s)
+        m.kc[bt[pos // m.ps], pos % m.ps] = o.widen(k, kv_dtype)[i]
+        m.vc[bt[pos // m.ps], pos % m.ps] = o.widen(v, kv_dtype)[i]
+    q = o.round_to(m.rng.standard_normal((n, m.H * group, m.D)).astype(np.float32), m.dtype)
+    tq, tk, tv = u.payload_to_torch(q, m.dtype), u.payload_to_torch(k, kv_dtype), u.payload_to_torch(v, kv_dtype)
+    if not host:
+        tq, tk, tv = tq.to(DEV), tk.to(DEV), tv.to(DEV)
+    out = m.pool.decode(seqs, tq, k_new=tk, v_new=tv, split_tokens=split)
+    table = np.stack([m.model.block_table(s) for s in seqs])
+    lens = np.array([m.model.seq_len(s) for s in seqs], np.int32)
+    kc, vc = (m.kc, m.vc) if group == 1 else (np.repeat(m.kc, group, axis=2), np.repeat(m.vc, group, axis=2))
+    want = o.paged_decode(o.widen(q, m.dtype), kc, vc, table, lens, 1.0 / np.sqrt(m.D))
+    u.assert_close(u.torch_to_f32(out), want, m.dtype, f"decode step lens={list(lens)}")
+    m.check_tables()
+    for i, s in enumerate(seqs):                                     # the token is in the pool, bit for bit
+        gk, gv = m.pool.gather(s, int(lens[i]) - 1, 1)
+        assert np.array_equal(u.torch_to_f32(gk)[0], o.widen(k, kv_dtype)[i]) and np.array_equal(u.torch_to_f32(gv)[0], o.widen(v, kv_dtype)[i])
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("D", [64, 128])
+def test_decode_step_folds_the_append_into_the_decode(dtype, D):
+    m = Mirror(num_pages=60, heads=3, head_dim=D, dtype=dtype, max_seqs=6, max_pages=16, seed=21)
+    a, b, c, d = m.create(), m.create(), m.create(), m.create()
+    m.append([a, b, c], [15, 16, 100])                 # a: the step fills a page; b: it opens one; d: its first token ever
+    for _ in range(3):                                 # three steps: slots 15, 16, 17 of a; page boundaries crossed
+        step_check(m, [a, b, c, d])
+    step_check(m, [c, a], split=32)                    # split-KV: the new token sits in the last chunk
+    m.decode_check([a, b, c, d])                       # a plain decode afterwards sees the same pool
+
+
+@pytest.mark.parametrize("group", [2, 3, 4, 8])
+def test_decode_step_grouped_query_attention(group):
+    m = Mirror(num_pages=40, heads=2, head_dim=128, dtype="f16", max_seqs=4, max_pages=16, seed=22)
+    a, b = m.create(), m.create()
+    m.append([a, b], [31, 77])
+    step_check(m, [a, b], group=group)
+    step_check(m, [b, a], group=group)
+
+
+@pytest.mark.parametrize("cfg", [dict(dtype="f32", page_size=16), dict(dtype="f16", page_size=8), dict(dtype="f16", page_size=16, kv="f32"),
+                                 dict(dtype="bf16", page_size=16, host=True)])
+def test_decode_step_general_path(cfg):
+    """Pools, element types and host tensors the fast kernels do not take: append, then decode, in one call."""
+    m = Mirror(num_pages=40, heads=2, head_dim=64, dtype=cfg["dtype"], page_size=cfg["page_size"], max_seqs=4, max_pages=16, seed=23)
+    a, b = m.create(), m.create()
+    m.append([a, b], [7, 40])
+    for _ in range(2):
+        step_check(m, [a, b], kv_dtype=cfg.get("kv"), host=cfg.get("host", False))
+
+
+def test_decode_step_refuses_what_append_refuses():
+    m = Mirror(num_pages=4, heads=1, head_dim=64, dtype="f16", max_seqs=4, max_pages=2, seed=24)
+    a = m.create()
+    m.append([a], [32])                                # the table row of a is full
+    z = torch.zeros((1, 1, 64), dtype=torch.float16, device=DEV)
+    with pytest.raises(abi.AhpcError) as e:
+        m.pool.decode([a], z, k_new=z, v_new=z)
+    assert e.value.status == 3
+    with pytest.raises(abi.AhpcError) as e:            # listed twice
+        m.pool.decode([a, a], torch.cat([z, z]), k_new=torch.cat([z, z]), v_new=torch.cat([z, z]))
+    assert e.value.status == 1
+    m.check_tables()                                   # nothing changed
+
+
 def test_block_tables_bit_exact_through_a_call_history():
     m = Mirror(num_pages=40, heads=2, head_dim=64, max_seqs=6, max_pages=12, seed=1)
     a, b, c = m.create(), m.create(), m.create()
