@@ -125,6 +125,27 @@ struct PagedPrefillLaunch {
     int device;
     cudaStream_t stream;
 };
+// Decode on the tensor cores for grouped-query attention (fa_tc.cu, called from paged_decode.cu): the query heads
+// that share a key/value head are the rows of one tile; partials go to the combine kernel's scratch.
+struct PagedDecodeTcLaunch {
+    const void* q;                // [n_seqs, q_heads, head_dim] in the pool's 16-bit type
+    int dtype;
+    int q_heads, kv_heads, head_dim;
+    int n_seqs;
+    const int32_t* seqs_dev;      // device copy of the call's sequence slots
+    const int32_t* seq_len;       // the pool's lengths
+    const void *k_data, *v_data;
+    const int32_t* table;
+    long long page_elems;
+    int num_pages, max_pages;
+    float* part_o;                // [n_seqs][2 * chunks][q_heads][head_dim]
+    float2* part_ml;              // [n_seqs][2 * chunks][q_heads]
+    int split, chunks;            // tokens per CTA (a multiple of 128), CTAs per (sequence, key/value head)
+    float scale;
+    int device;
+    cudaStream_t stream;
+};
+ahpc_status launch_decode_tc(const PagedDecodeTcLaunch& a);
 bool fa_paged_tc_supported(const PagedPrefillLaunch& a, const char** why);
 ahpc_status launch_fa_paged_tc(const PagedPrefillLaunch& a);
 

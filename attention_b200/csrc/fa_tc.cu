@@ -45,6 +45,10 @@ template <int D> struct Cfg {
     static constexpr int STAGES = D == 128 ? 4 : 8;          // K/V ring depth (tiles)
     static constexpr uint32_t SMEM_TILES = (2 + STAGES) * TILE_BYTES;
     static constexpr uint32_t SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    // decode: a deeper ring - that kernel lives on the bytes it keeps in flight
+    static constexpr int STAGES_DECODE = D == 128 ? 5 : 8;
+    static constexpr uint32_t SMEM_TILES_DECODE = (2 + STAGES_DECODE) * TILE_BYTES;
+    static constexpr uint32_t SMEM_BYTES_DECODE = SMEM_TILES_DECODE + 1024 + 256;
     static constexpr uint32_t O_COL = 256;                   // first column of O0
 };
 
@@ -55,7 +59,16 @@ struct PagedView {
     const int4* seqs;         // per listed sequence {slot, first query row in q/out, query rows, tokens held}
     long long page_elems;     // elements of K (or V) in one page
     int max_pages;
+    // decode (MODE_DECODE): one query token per listed sequence, the query heads of a key/value head as the rows of the tile
+    const int32_t* seq_ids;   // device copy of the call's sequence slots
+    const int32_t* seq_len;   // the pool's lengths
+    float* part_o;            // split-KV partials as paged_combine_kernel reads them: [n_seqs][parts][q_heads][head_dim]
+    float2* part_ml;          // [n_seqs][parts][q_heads] (reference maximum, sum), base 2
+    int split;                // tokens per CTA (a multiple of 128)
+    int parts;                // partial slots per sequence = 2 * chunks
 };
+
+enum { MODE_DENSE = 0, MODE_PREFILL = 1, MODE_DECODE = 2 };
 
 struct TcParams {
     void* out;
@@ -83,16 +96,34 @@ struct Barriers {        // one uint64 each, in shared memory
     int abort;
 };
 
-template <int D, bool BF16, bool PAGED>
+template <int D, bool BF16, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const TcParams p) {
     using C = Cfg<D>;
+    constexpr bool PAGED = MODE != MODE_DENSE, DECODE = MODE == MODE_DECODE;
+    constexpr int STAGES = DECODE ? C::STAGES_DECODE : C::STAGES;
+    constexpr uint32_t Q_TILES = 2, SMEM_TILES = DECODE ? C::SMEM_TILES_DECODE : C::SMEM_TILES;
     // Dense: the sizes of the call.  Paged: those of the sequence this CTA works on (grid.z), whose queries are its LAST
     // seq_q tokens: query row r sits at position r + c_off, which is what the causal rule compares with the key index.
     int seq_q = p.seq_q, seq_kv = p.seq_kv, c_off = p.causal_offset, row_base = 0, n_pairs = p.n_pairs;
     const int32_t* table_row = nullptr;
-    if constexpr (PAGED) {
+    int kv_base = 0;             // decode: first token of this CTA's chunk
+    if constexpr (DECODE) {
+        // grid (chunk, key/value head, sequence).  The tile's rows are the kv_group query heads that share this key/value
+        // head; the CTA's two tile slots take the chunk's key tiles alternately (even / odd), each with its own running
+        // maximum, sum and accumulator, and leave two partials for the combine kernel.  Slot 1 holds the heads 32 rows
+        // further down its tile (decode_shift): its rows then belong to another warp quadrant of tensor memory, so the
+        // exponentials of the two slots run on two different schedulers instead of queueing on one.
+        const int seq = p.paged.seq_ids[blockIdx.z];
+        const int len = p.paged.seq_len[seq];
+        kv_base = blockIdx.x * p.paged.split;
+        if (kv_base >= len) return;
+        seq_kv = min(len, kv_base + p.paged.split);
+        seq_q = p.kv_group; c_off = 0; n_pairs = 1;
+        row_base = blockIdx.z * p.heads + blockIdx.y * p.kv_group;
+        table_row = p.paged.table + (long long)seq * p.paged.max_pages;
+    } else if constexpr (PAGED) {
         const int4 info = p.paged.seqs[blockIdx.z];
         seq_q = info.z; seq_kv = info.w; c_off = seq_kv - seq_q; row_base = info.y;
         n_pairs = (seq_q + 2 * BM - 1) / (2 * BM);
@@ -103,13 +134,13 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t q_smem = smem_base;
-    const uint32_t ring_smem = smem_base + 2 * C::TILE_BYTES;
-    Barriers* bars = reinterpret_cast<Barriers*>(smem_aligned + C::SMEM_TILES);
+    const uint32_t ring_smem = smem_base + Q_TILES * C::TILE_BYTES;
+    Barriers* bars = reinterpret_cast<Barriers*>(smem_aligned + SMEM_TILES);
     volatile int* abort_flag = &bars->abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    const int total_pairs = PAGED ? n_pairs : p.n_pairs * p.batch * p.heads;
+    const int total_pairs = DECODE ? (int)gridDim.x : PAGED ? n_pairs : p.n_pairs * p.batch * p.heads;
     // second pass: did fa_fwd_tc2_kernel flag a tile of this pair?
     auto flagged = [&](int work) {
         const int bh_w = work / p.n_pairs, slot_w = work % p.n_pairs;
@@ -149,13 +180,16 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // Consecutive work numbers are the pairs of ONE (batch, head), so the CTAs resident at any time share a few K/V
     // streams and those stay in L2; heavy (late) pairs first when causal.
     const int bh = PAGED ? (int)blockIdx.y : work / p.n_pairs, pair_slot = PAGED ? work : work % p.n_pairs;
-    const int pair = p.causal ? n_pairs - 1 - pair_slot : pair_slot;
+    const int pair = DECODE ? 0 : p.causal ? n_pairs - 1 - pair_slot : pair_slot;
     const int b = PAGED ? 0 : bh / p.heads, h = PAGED ? bh : bh % p.heads;
     const int q0 = pair * 2 * BM;
-    const int n_t0 = kv_tiles_for(q0, seq_q, seq_kv, p.causal, c_off);
-    const int n_t1 = kv_tiles_for(q0 + BM, seq_q, seq_kv, p.causal, c_off);
-    const int n_kv = max(n_t0, n_t1);
-    const int n_pages = (seq_kv + 15) >> 4;                  // paged: pages of the sequence (16 tokens each)
+    const int n_chunk_tiles = (seq_kv - kv_base + BN - 1) / BN;                        // decode: key tiles of this CTA's chunk
+    const int n_t0 = DECODE ? (n_chunk_tiles + 1) / 2 : kv_tiles_for(q0, seq_q, seq_kv, p.causal, c_off);
+    const int n_t1 = DECODE ? n_chunk_tiles / 2 : kv_tiles_for(q0 + BM, seq_q, seq_kv, p.causal, c_off);
+    const int n_kv = DECODE ? n_chunk_tiles : max(n_t0, n_t1);
+    const int n_pages = (seq_kv + 15) >> 4;                  // paged: pages up to the last key this CTA reads (16 tokens each)
+    const int page_base = kv_base >> 4;
+    const int decode_shift = DECODE && p.kv_group <= BM - 32 ? 32 : 0;      // rows the heads sit down by in tile slot 1
 
     if (threadIdx.x == MMA_WARP * 32) {
         for (int t = 0; t < 2; ++t) {
@@ -165,7 +199,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             mbar_init(smem_u32(&bars->p[t]), BM);
             mbar_init(smem_u32(&bars->o[t]), 1);
         }
-        for (int s = 0; s < C::STAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             if (!first_round) { mbar_inval(smem_u32(&bars->full[s])); mbar_inval(smem_u32(&bars->empty[s])); }
             mbar_init(smem_u32(&bars->full[s]), 1);
             mbar_init(smem_u32(&bars->empty[s]), 1);
@@ -184,8 +218,10 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 if ((t == 0 ? n_t0 : n_t1) == 0) continue;
                 const uint32_t bar = smem_u32(&bars->q[t]);
                 mbar_expect_tx(bar, C::TILE_BYTES);
+                // decode: the same heads for both slots, slot 1 starting decode_shift rows earlier (rows before the tensor read as zero)
+                const int first_row = DECODE ? row_base - t * decode_shift : row_base + q0 + t * BM;
                 for (int sub = 0; sub < C::SUBTILES; ++sub)
-                    tma_load_4d(q_smem + t * C::TILE_BYTES + sub * C::SUB_BYTES, &map_q, bar, sub * 64, row_base + q0 + t * BM, h, b);
+                    tma_load_4d(q_smem + t * C::TILE_BYTES + sub * C::SUB_BYTES, &map_q, bar, sub * 64, first_row, DECODE ? 0 : h, b);
             }
         }
         int issued = 0;
@@ -196,15 +232,15 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // per 128-byte column block of its values.  Pages past the end of the sequence are not copied: their keys
             // are masked and their part of P V is never issued.
             constexpr uint32_t PAGE_BYTES = 16 * D * 2;
-            const int kvh = h / p.kv_group;
+            const int kvh = DECODE ? h : h / p.kv_group;
             int page = 0;
             for (int idx = 0; idx < 2 * n_kv; ++idx) {
-                const int slot = idx % C::STAGES, round = idx / C::STAGES;
+                const int slot = idx % STAGES, round = idx / STAGES;
                 if (round > 0) ok = wait_bounded(smem_u32(&bars->empty[slot]), (round - 1) & 1, abort_flag, p.error_word, 100 + slot);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&bars->full[slot]);
-                const int first = (idx >> 1) * (BN / 16), valid = min(BN / 16, n_pages - first);
+                const int first = page_base + (idx >> 1) * (BN / 16), valid = min(BN / 16, n_pages - first);
                 if (lane == 0) mbar_expect_tx(bar, valid * PAGE_BYTES);
                 if (idx & 1) {
                     if (lane < valid)
@@ -221,7 +257,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
         } else if (lane == 0) {
             for (int idx = 0; idx < 2 * n_kv && ok; ++idx) {
-                const int slot = idx % C::STAGES, round = idx / C::STAGES;
+                const int slot = idx % STAGES, round = idx / STAGES;
                 if (round > 0) ok = wait_bounded(smem_u32(&bars->empty[slot]), (round - 1) & 1, abort_flag, p.error_word, 100 + slot);
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&bars->full[slot]);
@@ -234,8 +270,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         if (!ok && lane == 0) {
             // Leave no copy in flight: wait (bounded) for the loads of the last ring round issued.
-            for (int idx = max(0, issued - C::STAGES); idx < issued; ++idx) {
-                const int slot = idx % C::STAGES, round = idx / C::STAGES;
+            for (int idx = max(0, issued - STAGES); idx < issued; ++idx) {
+                const int slot = idx % STAGES, round = idx / STAGES;
                 long long t0 = clock64();
                 while (!mbar_try_wait(smem_u32(&bars->full[slot]), round & 1) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
             }
@@ -247,6 +283,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             constexpr uint32_t IDESC_O = idesc_f16(BF16 ? 1 : 0, BM, D, 0, 1);      // P (TMEM)    x V (MN-major)
             const int n_t[2] = {n_t0, n_t1};
             bool ok = true;
+            bool n_kv_done = false;      // the decode order below has walked the key tiles
 
             // S_t = Q_t K_j^T : head_dim/16 MMAs of K = 16
             auto issue_s = [&](int t, int slot) {
@@ -275,27 +312,57 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tc_commit(smem_u32(&bars->o[t]));
             };
 
-            for (int t = 0; t < 2 && ok; ++t)
+            if constexpr (DECODE) {
+                // Key tile j belongs to tile slot j & 1.  Order on the pipe: S(0) S(1) | PV(0) S(2) | PV(1) S(3) | ...
+                for (int j = 0; j < 2 && j < n_kv && ok; ++j) {
+                    const int idx_k = 2 * j, slot_k = idx_k % STAGES;
+                    ok = wait_bounded(smem_u32(&bars->q[j]), 0, abort_flag, p.error_word, 200 + j);
+                    if (ok) ok = wait_bounded(smem_u32(&bars->full[slot_k]), (idx_k / STAGES) & 1, abort_flag, p.error_word, 210);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_s(j, slot_k);
+                    tc_commit(smem_u32(&bars->empty[slot_k]));
+                }
+                for (int j = 0; j < n_kv && ok; ++j) {
+                    const int t = j & 1, idx_v = 2 * j + 1, slot_v = idx_v % STAGES;
+                    ok = wait_bounded(smem_u32(&bars->full[slot_v]), (idx_v / STAGES) & 1, abort_flag, p.error_word, 220);
+                    if (ok) ok = wait_bounded(smem_u32(&bars->p[t]), (j >> 1) & 1, abort_flag, p.error_word, 240 + t);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_o(t, slot_v, j < 2, min(BN / 16, n_pages - page_base - j * (BN / 16)));
+                    tc_commit(smem_u32(&bars->empty[slot_v]));
+                    if (j + 2 < n_kv) {
+                        const int idx_k = 2 * (j + 2), slot_k = idx_k % STAGES;
+                        ok = wait_bounded(smem_u32(&bars->full[slot_k]), (idx_k / STAGES) & 1, abort_flag, p.error_word, 230);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_s(t, slot_k);
+                        tc_commit(smem_u32(&bars->empty[slot_k]));
+                    }
+                }
+                n_kv_done = true;
+            }
+            for (int t = 0; t < 2 && ok && !n_kv_done; ++t)
                 if (n_t[t] > 0) ok = wait_bounded(smem_u32(&bars->q[t]), 0, abort_flag, p.error_word, 200 + t);
-            if (ok) ok = wait_bounded(smem_u32(&bars->full[0]), 0, abort_flag, p.error_word, 210);
-            if (ok) {
+            if (ok && !n_kv_done) ok = wait_bounded(smem_u32(&bars->full[0]), 0, abort_flag, p.error_word, 210);
+            if (ok && !n_kv_done) {
                 tc_fence_after_sync();
                 for (int t = 0; t < 2; ++t)
                     if (n_t[t] > 0) issue_s(t, 0);
                 tc_commit(smem_u32(&bars->empty[0]));
             }
-            for (int j = 0; j < n_kv && ok; ++j) {
+            for (int j = 0; j < n_kv && ok && !n_kv_done; ++j) {
                 const int idx_v = 2 * j + 1, idx_k = 2 * j + 2;
-                const int slot_v = idx_v % C::STAGES, slot_k = idx_k % C::STAGES;
+                const int slot_v = idx_v % STAGES, slot_k = idx_k % STAGES;
                 const bool more = j + 1 < n_kv;
-                ok = wait_bounded(smem_u32(&bars->full[slot_v]), (idx_v / C::STAGES) & 1, abort_flag, p.error_word, 220);
-                if (ok && more) ok = wait_bounded(smem_u32(&bars->full[slot_k]), (idx_k / C::STAGES) & 1, abort_flag, p.error_word, 230);
+                ok = wait_bounded(smem_u32(&bars->full[slot_v]), (idx_v / STAGES) & 1, abort_flag, p.error_word, 220);
+                if (ok && more) ok = wait_bounded(smem_u32(&bars->full[slot_k]), (idx_k / STAGES) & 1, abort_flag, p.error_word, 230);
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j < n_t[t]) {
                         ok = wait_bounded(smem_u32(&bars->p[t]), j & 1, abort_flag, p.error_word, 240 + t);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        issue_o(t, slot_v, j == 0, min(BN / 16, n_pages - j * (BN / 16)));
+                        issue_o(t, slot_v, j == 0, min(BN / 16, n_pages - page_base - j * (BN / 16)));
                     }
                     if (j + 1 < n_t[t]) issue_s(t, slot_k);
                 }
@@ -308,7 +375,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // another pair (commits complete in order, so this covers the earlier ones too).
             if (ok && p.redo) {
                 const int idx_last = 2 * (n_kv - 1) + 1;
-                ok = wait_bounded(smem_u32(&bars->empty[idx_last % C::STAGES]), (idx_last / C::STAGES) & 1, abort_flag, p.error_word, 250);
+                ok = wait_bounded(smem_u32(&bars->empty[idx_last % STAGES]), (idx_last / STAGES) & 1, abort_flag, p.error_word, 250);
             }
         }
     } else {
@@ -316,15 +383,44 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int t = warp >> 2;                               // query tile of this warpgroup
         const int n_mine = t == 0 ? n_t0 : n_t1;
         const int r_in_tile = (warp & 3) * 32 + lane;
-        const int row = q0 + t * BM + r_in_tile;
+        const int row = DECODE ? r_in_tile - t * decode_shift : q0 + t * BM + r_in_tile;    // decode: the query head of the group
+        const bool row_valid = row >= 0 && row < seq_q;
+        // decode: a warp none of whose rows is a query head keeps step with the barriers and does nothing else
+        const bool warp_idle = DECODE && ((warp & 3) * 32 + 31 - t * decode_shift < 0 || (warp & 3) * 32 - t * decode_shift >= seq_q);
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t s_addr = tmem + lane_base + t * BN;
         const uint32_t o_addr = tmem + lane_base + C::O_COL + t * D;
         float m_used = -INFINITY, l_run = 0.f;
         bool ok = true;
 
-        for (int j = 0; j < n_mine; ++j) {
-            ok = wait_bounded(smem_u32(&bars->s[t]), j & 1, abort_flag, p.error_word, 300 + t);
+        // The sequence's last page may hold slots nobody wrote: their probabilities are zero, but zero times whatever bits
+        // lie there need not be zero.  The slot's threads clear those value rows in shared memory before P V reads them.
+        auto clear_unwritten_value_rows = [&](int j) -> bool {
+            const int k0 = kv_base + j * BN;
+            if (k0 + BN > seq_kv && (seq_kv & 15)) {
+                const int idx_v = 2 * j + 1, slot_v = idx_v % STAGES;
+                if (!wait_bounded(smem_u32(&bars->full[slot_v]), (idx_v / STAGES) & 1, abort_flag, p.error_word, 320 + t)) return false;
+                const int first_row = seq_kv - k0, rows = 16 - (seq_kv & 15);
+                uint8_t* vt = smem_aligned + Q_TILES * C::TILE_BYTES + slot_v * C::TILE_BYTES;
+                for (int c = r_in_tile; c < rows * (D / 8); c += BM) {
+                    const int r = first_row + c / (D / 8), piece = c % (D / 8);
+                    *reinterpret_cast<uint4*>(vt + (piece >> 3) * C::SUB_BYTES + r * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                fence_proxy_async();
+            }
+            return true;
+        };
+
+        if (warp_idle) {
+            for (int jj = 0; jj < n_mine && ok; ++jj) {
+                ok = wait_bounded(smem_u32(&bars->s[t]), jj & 1, abort_flag, p.error_word, 300 + t);
+                if (ok) ok = clear_unwritten_value_rows(2 * jj + t);
+                if (ok) mbar_arrive(smem_u32(&bars->p[t]));
+            }
+        }
+        for (int jj = 0; jj < n_mine && !warp_idle; ++jj) {
+            const int j = DECODE ? 2 * jj + t : jj;                // the key tile: in decode the slots take them alternately
+            ok = wait_bounded(smem_u32(&bars->s[t]), jj & 1, abort_flag, p.error_word, 300 + t);
             if (!ok) break;
             tc_fence_after_sync();
             uint32_t sr[4][32];
@@ -332,7 +428,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr[c]);
             tmem_wait_ld();
 
-            const int k0 = j * BN;
+            const int k0 = kv_base + j * BN;
             const bool need_mask = (p.causal && k0 + BN - 1 > q0 + t * BM + c_off) || (k0 + BN > seq_kv);
             if (need_mask) {
                 const int limit = p.causal ? min(seq_kv - 1, row + c_off) : seq_kv - 1;     // last visible key
@@ -341,20 +437,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     if (k0 + k > limit) sr[k >> 5][k & 31] = 0xff800000u;            // -inf
             }
             if constexpr (PAGED) {
-                // The sequence's last page may hold slots nobody wrote: their probabilities are zero, but zero times
-                // whatever bits lie there need not be zero.  Clear those value rows in shared memory before P V reads them.
-                if (k0 + BN > seq_kv && (seq_kv & 15)) {
-                    const int idx_v = 2 * j + 1, slot_v = idx_v % C::STAGES;
-                    ok = wait_bounded(smem_u32(&bars->full[slot_v]), (idx_v / C::STAGES) & 1, abort_flag, p.error_word, 320 + t);
-                    if (!ok) break;
-                    const int first_row = seq_kv - k0, rows = 16 - (seq_kv & 15);
-                    uint8_t* vt = smem_aligned + 2 * C::TILE_BYTES + slot_v * C::TILE_BYTES;
-                    for (int c = r_in_tile; c < rows * (D / 8); c += BM) {
-                        const int r = first_row + c / (D / 8), piece = c % (D / 8);
-                        *reinterpret_cast<uint4*>(vt + (piece >> 3) * C::SUB_BYTES + r * 128 + (piece & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    fence_proxy_async();
-                }
+                ok = clear_unwritten_value_rows(j);
+                if (!ok) break;
             }
             if (!PAGED && p.mask && row < p.seq_q) {
                 // explicit mask: this thread's row, the 128 keys of this tile
@@ -388,7 +472,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             const float row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
-            if (j == 0) {
+            if (jj == 0) {
                 m_used = row_max;
             } else {
                 const bool grow = (row_max - m_used) * p.scale_log2 > RESCALE_THRESHOLD;   // -inf cases: false or inf>thr
@@ -439,8 +523,30 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             mbar_arrive(smem_u32(&bars->p[t]));
         }
 
-        if (ok && n_mine > 0) ok = wait_bounded(smem_u32(&bars->o[t]), (n_mine - 1) & 1, abort_flag, p.error_word, 310 + t);
-        if (ok && n_mine > 0) {
+        if (ok && n_mine > 0 && !warp_idle) ok = wait_bounded(smem_u32(&bars->o[t]), (n_mine - 1) & 1, abort_flag, p.error_word, 310 + t);
+        if constexpr (DECODE) {
+            // This slot's partial for the combine kernel: accumulator as it stands, its sum, and the maximum it refers to
+            // in base-2 units.  Slot 1 of a one-tile chunk has nothing: an empty partial.
+            if (ok && !warp_idle) {
+                const long long part = ((long long)blockIdx.z * p.paged.parts + 2 * blockIdx.x + t) * p.heads + row_base - (long long)blockIdx.z * p.heads + row;
+                if (n_mine > 0) tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t orow[32];
+                    if (n_mine > 0) {                      // warp-uniform
+                        tmem_ld32(o_addr + c * 32, orow);
+                        tmem_wait_ld();
+                        if (row_valid) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                *reinterpret_cast<uint4*>(p.paged.part_o + part * D + c * 32 + i * 4) = make_uint4(orow[4 * i], orow[4 * i + 1], orow[4 * i + 2], orow[4 * i + 3]);
+                        }
+                    }
+                }
+                if (row_valid)
+                    p.paged.part_ml[part] = n_mine > 0 ? make_float2(m_used * p.scale_log2, l_run) : make_float2(-INFINITY, 0.f);
+            }
+        } else if (ok && n_mine > 0) {
             tc_fence_after_sync();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             uint16_t* orow_g = static_cast<uint16_t*>(p.out) + b * p.os[0] + h * p.os[1] + (long long)(row_base + row) * p.os[2];
@@ -479,7 +585,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 template <int D, bool BF16>
 ahpc_status launch(const FaLaunch& a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcParams& p) {
     using C = Cfg<D>;
-    auto kernel = fa_fwd_tc_kernel<D, BF16, false>;
+    auto kernel = fa_fwd_tc_kernel<D, BF16, MODE_DENSE>;
     AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
     long long ctas = (long long)p.n_pairs * a.batch * a.heads;
     if (p.redo) ctas = std::min<long long>(ctas, std::max(1, sm_count(a.device)));      // second pass: one CTA per SM walks the flags
@@ -649,12 +755,57 @@ ahpc_status launch_two_tile(const FaLaunch& a, const int* redo, int* item_counte
 template <int D, bool BF16>
 ahpc_status launch_paged(const PagedPrefillLaunch& a, const CUtensorMap& mq, const CUtensorMap& mv, const TcParams& p) {
     using C = Cfg<D>;
-    auto kernel = fa_fwd_tc_kernel<D, BF16, true>;
+    auto kernel = fa_fwd_tc_kernel<D, BF16, MODE_PREFILL>;
     AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES));
     const dim3 grid((unsigned)((a.max_q + 2 * BM - 1) / (2 * BM)), (unsigned)a.q_heads, (unsigned)a.n_seqs);
     kernel<<<grid, TC_THREADS, C::SMEM_BYTES, a.stream>>>(mq, mq /*no dense key map*/, mv, p);
     AHPC_CUDA_OK(cudaGetLastError());
     return AHPC_SUCCESS;
+}
+
+template <int D, bool BF16>
+ahpc_status launch_decode_mode(const PagedDecodeTcLaunch& a, const CUtensorMap& mq, const CUtensorMap& mv, const TcParams& p) {
+    using C = Cfg<D>;
+    auto kernel = fa_fwd_tc_kernel<D, BF16, MODE_DECODE>;
+    AHPC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES_DECODE));
+    const dim3 grid((unsigned)a.chunks, (unsigned)a.kv_heads, (unsigned)a.n_seqs);
+    kernel<<<grid, TC_THREADS, C::SMEM_BYTES_DECODE, a.stream>>>(mq, mq /*no dense key map*/, mv, p);
+    AHPC_CUDA_OK(cudaGetLastError());
+    return AHPC_SUCCESS;
+}
+
+// One query token per listed sequence, grouped-query attention: per (chunk of the context, key/value head, sequence) one
+// CTA whose tile rows are the query heads of the group.  Leaves 2 * chunks partials per (sequence, query head).
+ahpc_status launch_decode_tc(const PagedDecodeTcLaunch& a) {
+    CUtensorMap mq, mv;
+    const long long rows = (long long)a.n_seqs * a.q_heads;
+    const int64_t qs[4] = {rows * a.head_dim, rows * a.head_dim, a.head_dim, 1};
+    const int64_t vs[4] = {a.page_elems, 16ll * a.head_dim, a.head_dim, 1};
+    AHPC_TRY(make_map(&mq, a.q, a.dtype, 1, 1, (int)rows, a.head_dim, qs));
+    AHPC_TRY(make_map(&mv, a.v_data, a.dtype, a.num_pages, a.kv_heads, 16, a.head_dim, vs, 16));
+    TcParams p{};
+    p.batch = 1; p.heads = a.q_heads; p.seq_q = a.q_heads / a.kv_heads; p.seq_kv = 0;
+    p.scale = a.scale;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.causal = 0;
+    p.n_pairs = 1;
+    p.kv_group = a.q_heads / a.kv_heads;
+    p.n_tiles = 1;
+    p.bh_group = 1;
+    p.paged.k_data = static_cast<const uint16_t*>(a.k_data);
+    p.paged.table = a.table;
+    p.paged.page_elems = a.page_elems;
+    p.paged.max_pages = a.max_pages;
+    p.paged.seq_ids = a.seqs_dev;
+    p.paged.seq_len = a.seq_len;
+    p.paged.part_o = a.part_o;
+    p.paged.part_ml = a.part_ml;
+    p.paged.split = a.split;
+    p.paged.parts = 2 * a.chunks;
+    AHPC_TRY(error_word_for(a.device, &p.error_word));
+    const bool bf16 = a.dtype == AHPC_BF16;
+    if (a.head_dim == 128) return bf16 ? launch_decode_mode<128, true>(a, mq, mv, p) : launch_decode_mode<128, false>(a, mq, mv, p);
+    return bf16 ? launch_decode_mode<64, true>(a, mq, mv, p) : launch_decode_mode<64, false>(a, mq, mv, p);
 }
 
 bool fa_paged_tc_supported(const PagedPrefillLaunch& a, const char** why) {

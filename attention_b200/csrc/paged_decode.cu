@@ -18,6 +18,8 @@
 #include <cstdlib>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -49,6 +51,9 @@ struct DecodeParams {
     // pool's type.  The kernels read that token from here instead of the pool, and one CTA per key/value head stores it.
     const void* new_k;
     const void* new_v;
+    int parts_per_chunk;       // partials a chunk leaves for the combine: 1, or 2 from the tensor-core decode
+    int use_tc;                // the tensor-core decode of fa_tc.cu writes the partials (grouped-query attention)
+    float scale;
 };
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
@@ -446,7 +451,7 @@ __global__ void paged_combine_kernel(const DecodeParams p) {
     const int head = blockIdx.x, si = blockIdx.y;
     const int seq = p.seqs[si];
     const int len = p.seq_len[seq];
-    const int n_chunks = (len + p.split - 1) / p.split;
+    const int n_chunks = (len + p.split - 1) / p.split * p.parts_per_chunk;
     const int D = p.head_dim;
     const size_t base = (size_t)si * p.max_chunks * p.heads + head;
     float m_all = -INFINITY;
@@ -519,12 +524,40 @@ int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, in
     return split;
 }
 
+// AHPC_DECODE_KERNEL=simt keeps grouped-query decodes on the FP32 kernels, =tc sends every eligible call (any group
+// size) to the tensor-core decode; unset, groups of more than 4 query heads per key/value head go there.
+int decode_kernel_choice() {
+    static const int choice = [] {
+        const char* e = std::getenv("AHPC_DECODE_KERNEL");
+        if (!e) return 0;
+        return std::strcmp(e, "simt") == 0 ? 1 : std::strcmp(e, "tc") == 0 ? 2 : 0;
+    }();
+    return choice;
+}
+bool tc_decode_eligible(const ahpc_pool* p, int q_heads, int qo_dtype, int requested_split) {
+    const int group = q_heads / p->cfg.heads, choice = decode_kernel_choice();
+    if (!fast_path(p) || qo_dtype != p->cfg.dtype || group > 128 || choice == 1) return false;
+    if (requested_split > 0 && requested_split % 128 != 0) return false;
+    return choice == 2 || group > 4;        // a group of 4 runs as fast on paged_decode_gqa_kernel (measured), larger ones do not
+}
+
 template <typename T, typename TQ>
 ahpc_status launch_decode(const ahpc_pool* pool, const DecodeParams& dp, cudaStream_t st) {
     dim3 grid(dp.max_chunks, dp.heads, dp.n_seqs);
     bool launched = false;
+    if (dp.use_tc) {
+        PagedDecodeTcLaunch l{};
+        l.q = dp.q; l.dtype = pool->cfg.dtype;
+        l.q_heads = dp.heads; l.kv_heads = dp.kv_heads; l.head_dim = dp.head_dim; l.n_seqs = dp.n_seqs;
+        l.seqs_dev = dp.seqs; l.seq_len = dp.seq_len; l.k_data = dp.k_data; l.v_data = dp.v_data; l.table = dp.table;
+        l.page_elems = (long long)dp.page_elems; l.num_pages = pool->cfg.num_pages; l.max_pages = dp.max_pages;
+        l.part_o = dp.part_o; l.part_ml = dp.part_ml; l.split = dp.split; l.chunks = dp.max_chunks / 2;
+        l.scale = dp.scale; l.device = pool->cfg.device; l.stream = st;
+        AHPC_TRY(launch_decode_tc(l));
+        launched = true;
+    }
     if constexpr (sizeof(T) == 2) {
-        if (fast_path(pool)) {
+        if (!launched && fast_path(pool)) {
             // grouped-query kernels: one CTA per G query heads of a group
 #define AHPC_GQA_LAUNCH(G)                                                                                   \
     do {                                                                                                     \
@@ -616,11 +649,24 @@ static ahpc_status decode_locked(const ahpc_decode_args* a, int q_heads, const v
         max_len = std::max(max_len, p->h_len[s]);
     }
     const int ps = p->cfg.page_size;
-    int split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device), cta_heads(p, q_heads));
+    const bool use_tc = new_k == nullptr && tc_decode_eligible(p, q_heads, a->qo_dtype, a->split_tokens);
+    int split;
+    if (use_tc) {
+        // One CTA per (chunk, key/value head, sequence) fills an SM: long chunks, halved until the grid holds two rounds.
+        split = a->split_tokens > 0 ? a->split_tokens : 2048;
+        while (a->split_tokens <= 0 && split > 256) {
+            int64_t ctas = 0;
+            for (int i = 0; i < a->n_seqs; ++i) ctas += (p->h_len[a->seqs[i]] + split - 1) / split;
+            if (ctas * p->cfg.heads >= 2 * (int64_t)sm_count(p->cfg.device)) break;
+            split /= 2;
+        }
+    } else {
+        split = pick_split(p, a->seqs, a->n_seqs, a->split_tokens, sm_count(p->cfg.device), cta_heads(p, q_heads));
+    }
     if (split % ps) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: split_tokens %d is not a multiple of the page size %d", split, ps);
     if (!fast_path(p) && split > GEN_MAX_SPLIT)
         return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_decode: split_tokens %d exceeds %d for this pool configuration", split, GEN_MAX_SPLIT);
-    const int max_chunks = std::max(1, (max_len + split - 1) / split);
+    const int max_chunks = std::max(1, (max_len + split - 1) / split) * (use_tc ? 2 : 1);      // partial slots per sequence
     if (max_chunks > 2147483647 / 1) return fail(AHPC_INTERNAL_ERROR, "ahpc_paged_decode: chunk count overflow");
 
     const ScratchLayout lay = scratch_layout(a->n_seqs, max_chunks, q_heads, p->cfg.head_dim);
@@ -658,6 +704,7 @@ static ahpc_status decode_locked(const ahpc_decode_args* a, int q_heads, const v
     const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);
     dp.scale_log2 = scale * LOG2E;
     dp.new_k = new_k; dp.new_v = new_v;
+    dp.parts_per_chunk = use_tc ? 2 : 1; dp.use_tc = use_tc ? 1 : 0; dp.scale = scale;
 
     ahpc_status s;
     if (p->cfg.dtype == AHPC_F32) s = launch_decode_q<float>(p, dp, a->qo_dtype, st);
@@ -699,7 +746,7 @@ ahpc_status ahpc_paged_decode_step(const ahpc_decode_args* a, const void* k_new,
     ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
     // The fast kernels can take the new token straight from the caller's tensors and store it on their way; everything
     // else (other pool layouts, another element type, host tensors) appends first and decodes afterwards.
-    const bool fold = fast_path(p) && kv_dtype == p->cfg.dtype && !is_host_pointer(k_new) && !is_host_pointer(v_new) &&
+    const bool fold = !tc_decode_eligible(p, q_heads, a->qo_dtype, a->split_tokens) && fast_path(p) && kv_dtype == p->cfg.dtype && !is_host_pointer(k_new) && !is_host_pointer(v_new) &&
                       reinterpret_cast<uintptr_t>(k_new) % 16 == 0 && reinterpret_cast<uintptr_t>(v_new) % 16 == 0;
     const std::vector<int32_t> ones((size_t)a->n_seqs, 1);
     AHPC_TRY(pool_append_locked(p, a->seqs, ones.data(), a->n_seqs, k_new, v_new, kv_dtype, (cudaStream_t)a->stream, !fold));
@@ -760,6 +807,7 @@ ahpc_status ahpc_paged_decode_static(const ahpc_decode_args* a) {
     const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);
     dp.scale_log2 = scale * LOG2E;
     dp.new_k = dp.new_v = nullptr;
+    dp.parts_per_chunk = 1; dp.use_tc = 0; dp.scale = scale;
     if (p->cfg.dtype == AHPC_F32) return launch_decode_q<float>(p, dp, a->qo_dtype, st);
     if (p->cfg.dtype == AHPC_F16) return launch_decode_q<__half>(p, dp, a->qo_dtype, st);
     return launch_decode_q<__nv_bfloat16>(p, dp, a->qo_dtype, st);

@@ -151,8 +151,9 @@ def test_decode_step_refuses_what_append_refuses():
     with pytest.raises(abi.AhpcError) as e:
         m.pool.decode([a], z, k_new=z, v_new=z)
     assert e.value.status == 3
+    b = m.create()
     with pytest.raises(abi.AhpcError) as e:            # listed twice
-        m.pool.decode([a, a], torch.cat([z, z]), k_new=torch.cat([z, z]), v_new=torch.cat([z, z]))
+        m.pool.decode([b, b], torch.cat([z, z]), k_new=torch.cat([z, z]), v_new=torch.cat([z, z]))
     assert e.value.status == 1
     m.check_tables()                                   # nothing changed
 
@@ -261,6 +262,31 @@ def test_decode_grouped_query_attention(group, dtype, D, ps):
     m.decode_check([c, a], group=group, split=32 if ps == 16 else 16)
     if dtype != "f32":
         m.decode_check([b, c], group=group, no_alloc=True)
+
+
+@pytest.mark.parametrize("group", [40, 128])
+def test_decode_large_groups_and_multi_query_attention(group):
+    """Groups that fill more than one warp quadrant of the tile, up to multi-query attention with 128 heads on one key/value head."""
+    m = Mirror(num_pages=30, heads=1, head_dim=64, dtype="f16", max_seqs=4, max_pages=20, seed=60 + group)
+    a, b = m.create(), m.create()
+    m.append([a, b], [300, 129])
+    m.decode_check([a, b], group=group)
+    m.decode_check([a], group=group, split=128)
+
+
+@pytest.mark.parametrize("group", [5, 8, 16])
+@pytest.mark.parametrize("dtype,D", [("f16", 128), ("bf16", 64)])
+def test_decode_grouped_query_attention_on_the_tensor_cores(group, dtype, D):
+    """Groups of more than 4 query heads per key/value head with q in the pool's type: the query heads of a group are the
+    rows of one MMA tile.  Contexts around the tile (128) and chunk sizes, one-tile chunks, an empty sequence."""
+    m = Mirror(num_pages=280, heads=2, head_dim=D, dtype=dtype, max_seqs=8, max_pages=140, seed=70 + group)
+    lens = [1, 127, 128, 129, 700, 2100, 0]
+    seqs = [m.create() for _ in lens]
+    m.append(seqs[:-1], lens[:-1])
+    m.decode_check(seqs, group=group)                      # the library's chunk size
+    m.decode_check(seqs[3:6], group=group, split=256)      # several chunks per sequence
+    m.decode_check(seqs[4:6], group=group, split=128)      # one-tile chunks: the second tile slot stays empty
+    m.decode_check(seqs[:6], group=group, scale=0.3)
 
 
 def test_decode_empty_sequence_gives_zeros():
