@@ -321,13 +321,15 @@ def bench_paged_prefill(torch, dist, cfg, args, rank: int, world: int, peaks, pe
     return res
 
 
-def build_decode_pool(torch, cfg, rank: int):
+def build_decode_pool(torch, cfg, rank: int, q_heads: int | None = None):
     """Pool filled with the configuration's sequences: pages dealt from the seeded permutation, prefixes
-    shared by fork when the configuration asks for sharing."""
+    shared by fork when the configuration asks for sharing.  cfg.heads are the pool's (key/value) heads;
+    q_heads (a multiple of them) the query's."""
     from attention_b200 import ops, synth
     plan = synth.sharing_plan(cfg)
     ps = cfg.page_size
     n = len(plan.ctx)
+    q_heads = q_heads or cfg.heads
     pages_needed = int(sum((int(plan.ctx[i]) - int(plan.prefix_tokens[i]) + ps - 1) // ps for i in range(n))) + 16
     pool = ops.KVPool(num_pages=pages_needed, heads=cfg.heads, head_dim=cfg.head_dim, dtype=torch.float16, page_size=ps,
                       max_seqs=n, max_pages_per_seq=(cfg.ctx_hi + ps - 1) // ps, device=torch.cuda.current_device(),
@@ -345,15 +347,23 @@ def build_decode_pool(torch, cfg, rank: int):
             m = min(8192, fresh - at)
             kv = torch.randn((2, m, cfg.heads, cfg.head_dim), generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
             pool.append([seqs[i]], [m], kv[0], kv[1])
-    q = torch.randn((n, cfg.heads, cfg.head_dim), generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
+    q = torch.randn((n, q_heads, cfg.head_dim), generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
     return pool, seqs, q, plan
 
 
 def bench_decode(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind):
     from attention_b200 import synth
-    pool, seqs, q, plan = build_decode_pool(torch, cfg, rank)
+    q_heads = cfg.heads
+    if args.decode_group > 1:
+        # grouped-query attention: the configuration's heads are the query heads, 1/group of them the pool's
+        import dataclasses
+        assert cfg.heads % args.decode_group == 0, "--decode-group must divide the configuration's heads"
+        cfg = dataclasses.replace(cfg, heads=cfg.heads // args.decode_group)
+    pool, seqs, q, plan = build_decode_pool(torch, cfg, rank, q_heads)
     out = torch.empty_like(q)
     by = synth.decode_algorithmic_bytes(cfg, plan)
+    by["total_unique"] += (q_heads - cfg.heads) * 2 * len(seqs) * cfg.head_dim * 2       # q and out of all query heads
+    by["total_logical"] += (q_heads - cfg.heads) * 2 * len(seqs) * cfg.head_dim * 2
 
     def step():
         pool.decode(seqs, q, out)
@@ -374,15 +384,16 @@ def bench_decode(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind
         "metric": "paged_decode_hbm_gbs", "unit": "GB/s", "value": gbs_rank * world,
         "tokens_per_s": len(seqs) * world / sec, "effective_gbs_logical": by["total_logical"] * world / sec / 1e9,
         "ms_per_step": ms_per_step, "dtype": "f16",
-        "config": {"workload": f"{cfg.name}: paged decode FP16 batch {cfg.batch} H{cfg.heads} D{cfg.head_dim} page {cfg.page_size}, "
+        "config": {"workload": f"{cfg.name}: paged decode FP16 batch {cfg.batch} H{q_heads}{'' if q_heads == cfg.heads else '/' + str(cfg.heads) + ' key-value heads'} D{cfg.head_dim} page {cfg.page_size}, "
                                f"context {'logU' if cfg.log_uniform else 'U'}[{cfg.ctx_lo},{cfg.ctx_hi}], seeded page permutation",
                    "tokens_in_context": int(plan.ctx.astype(np.int64).sum()), "shared_page_fraction": plan.shared_fraction,
                    "l2": "KV read per step (GBs) far exceeds the 126 MB L2"},
         "e2e": {"value": by["total_unique"] * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "tokens_per_s": len(seqs) * world / (ms_e2e * 1e-3),
                 "h2d_bytes_per_step": q.numel() * 2 + len(seqs) * 4, "d2h_bytes_per_step": q.numel() * 2, "ms_per_step": ms_e2e},
         "roofline": {"bound": "hbm", "achieved": gbs_rank, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs_rank / peaks["hbm_gbs"],
-                     "traffic": NCU_TRAFFIC["paged_decode_kernel_ratio"] * by["total_unique"], "peak_source": peak_kind, "frac_of_nominal_8000": gbs_rank / 8000.0,
-                     "kernel": "paged_decode_kernel (+ paged_combine_kernel in the same timed step)",
+                     "traffic": NCU_TRAFFIC["paged_decode_kernel_ratio"] * by["total_unique"] if args.decode_group == 1 else None, "peak_source": peak_kind, "frac_of_nominal_8000": gbs_rank / 8000.0,
+                     "kernel": ("paged_decode_kernel" if args.decode_group == 1 else "paged_decode_gqa_kernel" if args.decode_group <= 4
+                                else "fa_fwd_tc_kernel<MODE_DECODE>") + " (+ paged_combine_kernel in the same timed step)",
                      "bytes_per_launch": by["total_unique"]},
         "clocks": clk.summary(), "gpu_launches": 2 * args.steps,
     }
@@ -426,6 +437,8 @@ def main():
     ap.add_argument("--decode", choices=["c3", "c5"], default="c3",
                     help="paged-decode configuration: c3 (batch 64, U[512,8192]) or c5 (batch 256, logU[1024,32768], shared prefixes)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill-over-pages section")
+    ap.add_argument("--decode-group", type=int, default=1,
+                    help="grouped-query decode: the configuration's heads are the query heads, 1/GROUP of them key/value heads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--strong", action="store_true",
                     help="strong scaling: the heads of ONE configuration are split over the ranks (ahpc_shard_range) instead of "
@@ -476,7 +489,7 @@ def main():
     fa = bench_fa(torch, dist, cfg, args, rank, world, peaks, peak_kind)
     torch.cuda.empty_cache()
     pre = None
-    if not args.no_prefill and not args.profile_small:
+    if not args.no_prefill:
         pre = bench_paged_prefill(torch, dist, cfg, args, rank, world, peaks, peak_kind)
         torch.cuda.empty_cache()
     dec = None
