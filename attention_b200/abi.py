@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = [
     "ahpc_pool_live_seqs", "ahpc_pool_read_block_table", "ahpc_pool_read_seq_lens",
     "ahpc_pool_read_refcounts", "ahpc_pool_read_free_ring", "ahpc_pool_read_error_flag",
     "ahpc_paged_decode", "ahpc_paged_decode_step", "ahpc_paged_decode_scratch_bytes", "ahpc_paged_decode_static",
-    "ahpc_paged_decode_static_capacity", "ahpc_paged_prefill", "ahpc_shard_range",
+    "ahpc_paged_decode_static_capacity", "ahpc_paged_prefill", "ahpc_paged_prefill_append", "ahpc_shard_range",
 ]
 
 
@@ -145,6 +145,7 @@ def lib() -> C.CDLL:
     L.ahpc_paged_decode_scratch_bytes.argtypes = [vp, i32, i32, i32]
     L.ahpc_paged_decode_scratch_bytes.restype = C.c_size_t
     L.ahpc_paged_prefill.argtypes = [C.POINTER(PrefillArgs)]
+    L.ahpc_paged_prefill_append.argtypes = [C.POINTER(PrefillArgs), vp, vp, i32]
     L.ahpc_shard_range.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]
     _lib = L
     return L

@@ -54,44 +54,50 @@ ahpc_status prefill_by_gather(ahpc_pool* p, const ahpc_prefill_args* a, const st
 
 using namespace ahpc;
 
-extern "C" ahpc_status ahpc_paged_prefill(const ahpc_prefill_args* a) {
-    if (!a || !a->pool) return fail(AHPC_INVALID_INPUT, "ahpc_paged_prefill: NULL argument");
+// ahpc_paged_prefill, and with k/v given ahpc_paged_prefill_append: the listed sequences first gain n_query[i] tokens.
+static ahpc_status prefill_call(const ahpc_prefill_args* a, const char* who, const void* k, const void* v, int kv_dtype) {
+    const bool append = k != nullptr;
+    if (!a || !a->pool) return fail(AHPC_INVALID_INPUT, "%s: NULL argument", who);
     ahpc_pool* p = a->pool;
     if (a->n_seqs <= 0) return AHPC_SUCCESS;
-    if (!a->seqs || !a->n_query) return fail(AHPC_INVALID_INPUT, "ahpc_paged_prefill: seqs and n_query must not be NULL");
-    if (!dtype_valid(a->qo_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_prefill: unknown dtype %d", a->qo_dtype);
-    if (!std::isfinite(a->scale) || a->scale < 0.f) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_prefill: scale must be finite and not negative");
+    if (!a->seqs || !a->n_query) return fail(AHPC_INVALID_INPUT, "%s: seqs and n_query must not be NULL", who);
+    if (!dtype_valid(a->qo_dtype)) return fail(AHPC_INVALID_PARAMETERS, "%s: unknown dtype %d", who, a->qo_dtype);
+    if (!std::isfinite(a->scale) || a->scale < 0.f) return fail(AHPC_INVALID_PARAMETERS, "%s: scale must be finite and not negative", who);
     const int q_heads = a->q_heads > 0 ? a->q_heads : p->cfg.heads;
     if (a->q_heads < 0 || q_heads % p->cfg.heads != 0)
-        return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_prefill: q_heads (%d) must be a multiple of the pool's heads (%d)", a->q_heads, p->cfg.heads);
-    if (a->head_major && a->n_seqs != 1) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_prefill: head_major takes one sequence per call");
-    if (a->n_seqs > p->cfg.max_seqs) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_prefill: more sequences (%d) than the pool has slots (%d)", a->n_seqs, p->cfg.max_seqs);
+        return fail(AHPC_INVALID_PARAMETERS, "%s: q_heads (%d) must be a multiple of the pool's heads (%d)", who, a->q_heads, p->cfg.heads);
+    if (a->head_major && a->n_seqs != 1) return fail(AHPC_INVALID_PARAMETERS, "%s: head_major takes one sequence per call", who);
+    if (a->n_seqs > p->cfg.max_seqs) return fail(AHPC_INVALID_PARAMETERS, "%s: more sequences (%d) than the pool has slots (%d)", who, a->n_seqs, p->cfg.max_seqs);
+    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
+    cudaStream_t st = (cudaStream_t)a->stream;
 
     std::vector<SeqRun> runs((size_t)a->n_seqs);
+    std::vector<int> old_len((size_t)a->n_seqs, 0);
     long long total_q = 0;
-    int max_q = 0;
-    bool use_tc = false;
-    PagedPrefillLaunch l{};
     const float scale = a->scale != 0.0f ? a->scale : 1.0f / std::sqrt((float)p->cfg.head_dim);
     {
         std::lock_guard<std::mutex> lock(p->mu);
         for (int i = 0; i < a->n_seqs; ++i) {
             const int s = a->seqs[i], n = a->n_query[i];
-            if (s < 0 || s >= p->cfg.max_seqs || !p->h_live[s]) return fail(AHPC_INVALID_INPUT, "ahpc_paged_prefill: sequence %d not found", s);
-            if (n < 0 || n > p->h_len[s])
-                return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_prefill: %d query tokens for sequence %d, which holds %d", n, s, p->h_len[s]);
-            runs[i] = SeqRun{s, (int)total_q, n, p->h_len[s]};
+            if (s < 0 || s >= p->cfg.max_seqs || !p->h_live[s]) return fail(AHPC_INVALID_INPUT, "%s: sequence %d not found", who, s);
+            if (n < 0 || (!append && n > p->h_len[s]))
+                return fail(AHPC_INVALID_PARAMETERS, "%s: %d query tokens for sequence %d, which holds %d", who, n, s, p->h_len[s]);
+            old_len[i] = p->h_len[s];
             total_q += n;
-            max_q = std::max(max_q, n);
-            if (total_q > 2147483647ll) return fail(AHPC_UNSUPPORTED_OPERATION, "ahpc_paged_prefill: more than 2^31-1 query tokens");
+            if (total_q > 2147483647ll) return fail(AHPC_UNSUPPORTED_OPERATION, "%s: more than 2^31-1 query tokens", who);
+        }
+        if (total_q > 0 && (!a->q || !a->out)) return fail(AHPC_INVALID_INPUT, "%s: q and out must not be NULL", who);
+        if (append) AHPC_TRY(pool_append_locked(p, a->seqs, a->n_query, a->n_seqs, k, v, kv_dtype, st, true));
+        long long row = 0;
+        for (int i = 0; i < a->n_seqs; ++i) {
+            runs[i] = SeqRun{a->seqs[i], (int)row, a->n_query[i], p->h_len[a->seqs[i]]};
+            row += a->n_query[i];
         }
     }
     if (total_q == 0) return AHPC_SUCCESS;
-    if (!a->q || !a->out) return fail(AHPC_INVALID_INPUT, "ahpc_paged_prefill: q and out must not be NULL");
-    ScopedDevice device_guard_(p->cfg.device); AHPC_TRY(device_guard_.status());
-    cudaStream_t st = (cudaStream_t)a->stream;
 
-    const size_t qo_bytes = (size_t)total_q * q_heads * p->cfg.head_dim * dtype_size(a->qo_dtype);
+    const size_t es = dtype_size(a->qo_dtype);
+    const size_t qo_bytes = (size_t)total_q * q_heads * p->cfg.head_dim * es;
     const bool host_q = is_host_pointer(a->q), host_o = is_host_pointer(a->out);
     const void* dq = a->q;
     void* dout = a->out;
@@ -104,28 +110,66 @@ extern "C" ahpc_status ahpc_paged_prefill(const ahpc_prefill_args* a) {
     if (host_o) AHPC_TRY(staging_buffer(p->cfg.device, 8, qo_bytes, &dout));
 
     // [rows, heads, D], or for one sequence [heads, rows, D]
-    const int64_t token_stride = a->head_major ? p->cfg.head_dim : (int64_t)q_heads * p->cfg.head_dim;
-    const int64_t head_stride = a->head_major ? total_q * p->cfg.head_dim : p->cfg.head_dim;
-    l.q = dq; l.out = dout; l.token_stride = token_stride; l.head_stride = head_stride;
-    l.dtype = a->qo_dtype == p->cfg.dtype ? a->qo_dtype : -1;
-    l.q_heads = q_heads; l.kv_heads = p->cfg.heads; l.head_dim = p->cfg.head_dim; l.page_size = p->cfg.page_size;
-    l.total_q = total_q; l.max_q = max_q; l.n_seqs = a->n_seqs;
-    l.k_data = p->k_data; l.v_data = p->v_data; l.table = p->table;
-    l.page_elems = (long long)p->page_elems; l.num_pages = p->cfg.num_pages; l.max_pages = p->cfg.max_pages_per_seq;
-    l.scale = scale; l.causal = a->causal != 0; l.device = p->cfg.device; l.stream = st;
-    use_tc = fa_paged_tc_supported(l, nullptr);
+    const int D = p->cfg.head_dim;
+    const int64_t token_stride = a->head_major ? D : (int64_t)q_heads * D;
+    const int64_t head_stride = a->head_major ? total_q * D : D;
 
-    if (use_tc) {
-        std::lock_guard<std::mutex> lock(p->mu);
-        // {slot, first row, rows, tokens} per listed sequence, into the pool's per-call argument array
-        static_assert(sizeof(SeqRun) == sizeof(int4), "SeqRun is read as int4 on the device");
-        AHPC_CUDA_OK(cudaMemcpyAsync(p->call_args, runs.data(), runs.size() * sizeof(SeqRun), cudaMemcpyHostToDevice, st));
-        l.seqs_dev = reinterpret_cast<const int4*>(p->call_args);
-        AHPC_TRY(launch_fa_paged_tc(l));
-    } else {
-        AHPC_TRY(prefill_by_gather(p, a, runs, q_heads, scale, dq, dout, token_stride, head_stride));
+    // A sequence that held nothing before this call attends to exactly the tokens the caller has just handed over: that
+    // is a dense forward on the caller's own K/V, which the persistent kernel does faster than any walk over pages.
+    std::vector<SeqRun> paged;
+    paged.reserve(runs.size());
+    for (size_t i = 0; i < runs.size(); ++i) {
+        const SeqRun& r = runs[i];
+        if (r.rows == 0) continue;
+        bool dense = append && old_len[i] == 0 && kv_dtype == a->qo_dtype && !is_host_pointer(k) && !is_host_pointer(v);
+        if (dense) {
+            FaLaunch l{};
+            const int kvh = p->cfg.heads;
+            l.q = static_cast<const char*>(dq) + (size_t)r.first_row * token_stride * es;
+            l.out = static_cast<char*>(dout) + (size_t)r.first_row * token_stride * es;
+            l.k = static_cast<const char*>(k) + (size_t)r.first_row * kvh * D * es;
+            l.v = static_cast<const char*>(v) + (size_t)r.first_row * kvh * D * es;
+            l.dtype = a->qo_dtype; l.batch = 1; l.heads = q_heads; l.kv_heads = kvh; l.seq_q = r.rows; l.seq_kv = r.rows; l.head_dim = D;
+            const int64_t qs[4] = {(int64_t)r.rows * q_heads * D, head_stride, token_stride, 1};
+            const int64_t ks[4] = {(int64_t)r.rows * kvh * D, D, (int64_t)kvh * D, 1};
+            for (int d = 0; d < 4; ++d) { l.qs[d] = qs[d]; l.os[d] = qs[d]; l.ks[d] = ks[d]; l.vs[d] = ks[d]; }
+            l.scale = scale; l.causal = a->causal != 0; l.device = p->cfg.device; l.stream = st;
+            dense = fa_tc_supported(l, nullptr);
+            if (dense) AHPC_TRY(launch_fa_tc(l, AHPC_FA_KERNEL_TC));
+        }
+        if (!dense) paged.push_back(r);
+    }
+
+    if (!paged.empty()) {
+        PagedPrefillLaunch l{};
+        l.q = dq; l.out = dout; l.token_stride = token_stride; l.head_stride = head_stride;
+        l.dtype = a->qo_dtype == p->cfg.dtype ? a->qo_dtype : -1;
+        l.q_heads = q_heads; l.kv_heads = p->cfg.heads; l.head_dim = D; l.page_size = p->cfg.page_size;
+        l.total_q = total_q; l.n_seqs = (int)paged.size();
+        for (const SeqRun& r : paged) l.max_q = std::max(l.max_q, r.rows);
+        l.k_data = p->k_data; l.v_data = p->v_data; l.table = p->table;
+        l.page_elems = (long long)p->page_elems; l.num_pages = p->cfg.num_pages; l.max_pages = p->cfg.max_pages_per_seq;
+        l.scale = scale; l.causal = a->causal != 0; l.device = p->cfg.device; l.stream = st;
+        if (fa_paged_tc_supported(l, nullptr)) {
+            std::lock_guard<std::mutex> lock(p->mu);
+            // {slot, first row, rows, tokens} per sequence, into the pool's per-call argument array
+            static_assert(sizeof(SeqRun) == sizeof(int4), "SeqRun is read as int4 on the device");
+            AHPC_CUDA_OK(cudaMemcpyAsync(p->call_args, paged.data(), paged.size() * sizeof(SeqRun), cudaMemcpyHostToDevice, st));
+            l.seqs_dev = reinterpret_cast<const int4*>(p->call_args);
+            AHPC_TRY(launch_fa_paged_tc(l));
+        } else {
+            AHPC_TRY(prefill_by_gather(p, a, paged, q_heads, scale, dq, dout, token_stride, head_stride));
+        }
     }
     if (host_o) AHPC_CUDA_OK(cudaMemcpyAsync(a->out, dout, qo_bytes, cudaMemcpyDeviceToHost, st));
     if (host_q || host_o) AHPC_CUDA_OK(cudaStreamSynchronize(st));
     return AHPC_SUCCESS;
+}
+
+extern "C" ahpc_status ahpc_paged_prefill(const ahpc_prefill_args* a) { return prefill_call(a, "ahpc_paged_prefill", nullptr, nullptr, 0); }
+
+extern "C" ahpc_status ahpc_paged_prefill_append(const ahpc_prefill_args* a, const void* k, const void* v, int32_t kv_dtype) {
+    if (!k || !v) return fail(AHPC_INVALID_INPUT, "ahpc_paged_prefill_append: k and v must not be NULL");
+    if (!dtype_valid(kv_dtype)) return fail(AHPC_INVALID_PARAMETERS, "ahpc_paged_prefill_append: unknown kv dtype %d", kv_dtype);
+    return prefill_call(a, "ahpc_paged_prefill_append", k, v, kv_dtype);
 }

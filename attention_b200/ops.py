@@ -228,10 +228,12 @@ class KVPool:
         abi.check(fn(C.byref(a)))
         return out
 
-    def prefill(self, seqs, n_query, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, causal=True, head_major=False):
+    def prefill(self, seqs, n_query, q: torch.Tensor, out: torch.Tensor | None = None, *, scale=0.0, causal=True, head_major=False,
+                k_new: torch.Tensor | None = None, v_new: torch.Tensor | None = None):
         """The last n_query[i] tokens of each listed sequence (already appended) attend to what the pool holds for
         it.  q: [sum(n_query), q_heads, head_dim], the sequences' query tokens concatenated; returns out alike.
-        head_major=True (one sequence): q and out are [q_heads, n_query, head_dim]."""
+        head_major=True (one sequence): q and out are [q_heads, n_query, head_dim].
+        k_new, v_new ([sum(n_query), heads, head_dim]): these tokens are appended first (ahpc_paged_prefill_append)."""
         seqs, n_query = _i32(seqs), _i32(n_query)
         assert seqs.size == n_query.size
         tok, hd = (1, 0) if head_major else (0, 1)
@@ -244,5 +246,10 @@ class KVPool:
         a.pool, a.seqs, a.n_query, a.n_seqs = self._p, _pi32(seqs), _pi32(n_query), seqs.size
         a.q, a.out, a.qo_dtype, a.q_heads = q.data_ptr(), out.data_ptr(), _dtype_code(q), q.shape[hd]
         a.scale, a.causal, a.stream, a.head_major = float(scale), int(bool(causal)), self._stream(), int(bool(head_major))
+        if k_new is not None:
+            assert v_new is not None and k_new.is_contiguous() and v_new.is_contiguous() and k_new.dtype == v_new.dtype
+            assert tuple(k_new.shape) == (int(n_query.sum()), self.heads, self.head_dim) == tuple(v_new.shape)
+            abi.check(abi.lib().ahpc_paged_prefill_append(C.byref(a), k_new.data_ptr(), v_new.data_ptr(), _dtype_code(k_new)))
+            return out
         abi.check(abi.lib().ahpc_paged_prefill(C.byref(a)))
         return out

@@ -331,6 +331,18 @@ typedef struct ahpc_prefill_args {
 
 AHPC_API ahpc_status ahpc_paged_prefill(const ahpc_prefill_args* args);
 
+/* The hand-off from a prompt to the pool in one call: every listed sequence first gains its
+ * n_query[i] tokens (k, v: [sum(n_query), heads, head_dim] of the pool's heads in kv_dtype, as
+ * ahpc_pool_append takes them; no sequence listed twice) and then these tokens attend as in
+ * ahpc_paged_prefill.  A sequence that was empty before the call (a fresh prompt) attends to the
+ * caller's own k / v through the dense forward kernel; one with cached tokens (a later chunk, a
+ * shared prefix) reads its pages.  Replaces the temporary-sequence path of
+ * PagedAttention::forward (create, append_kv_cache, attend: paged_attention.cpp:132-174) when
+ * the sequence is to be kept.  Fails like ahpc_pool_append, changing nothing, when pages or
+ * table columns run out. */
+AHPC_API ahpc_status ahpc_paged_prefill_append(const ahpc_prefill_args* args, const void* k, const void* v,
+                                               int32_t kv_dtype);
+
 /* ------------------------------------------------------------------------------------------
  * Multi-GPU partitioning (host arithmetic only; no communication)
  * The (batch, head) pairs of a FlashAttention call, or the heads of a decode pool, are split

@@ -33,6 +33,12 @@ class Mirror:
         return a
 
     def append(self, seqs, counts, host=False):
+        tk, tv = self.stage(seqs, counts, host)
+        self.pool.append(seqs, counts, tk, tv)
+
+    def stage(self, seqs, counts, host=False):
+        """New tokens for the listed sequences: the CPU model and the canonical caches take them; returns the
+        tensors the device pool is to be given."""
         ks, vs = [], []
         for s, n in zip(seqs, counts):
             start = self.model.seq_len(s)
@@ -50,7 +56,7 @@ class Mirror:
         tv = u.payload_to_torch(np.concatenate(vs), self.dtype)
         if not host:
             tk, tv = tk.to(DEV), tv.to(DEV)
-        self.pool.append(seqs, counts, tk, tv)
+        return tk, tv
 
     def check_tables(self):
         for s in range(self.model.max_seqs):

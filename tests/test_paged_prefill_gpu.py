@@ -22,14 +22,16 @@ def sequence_kv(m: Mirror, seq: int, group: int = 1):
     return np.ascontiguousarray(k.transpose(1, 0, 2))[None], np.ascontiguousarray(v.transpose(1, 0, 2))[None]
 
 
-def prefill_check(m: Mirror, seqs, n_query, *, causal=True, group=1, qo_dtype=None, host=False, scale=0.0):
+def prefill_check(m: Mirror, seqs, n_query, *, causal=True, group=1, qo_dtype=None, host=False, scale=0.0, append=False):
+    """append=True: the query tokens are new - the call hands their K/V over as well (ahpc_paged_prefill_append)."""
     qo_dtype = qo_dtype or m.dtype
     total = int(sum(n_query))
+    new_kv = m.stage(seqs, n_query, host) if append else (None, None)
     q = o.round_to(m.rng.standard_normal((total, m.H * group, m.D)).astype(np.float32), qo_dtype)
     tq = u.payload_to_torch(q, qo_dtype)
     if not host:
         tq = tq.to(DEV)
-    out = u.torch_to_f32(m.pool.prefill(seqs, n_query, tq, causal=causal, scale=scale))
+    out = u.torch_to_f32(m.pool.prefill(seqs, n_query, tq, causal=causal, scale=scale, k_new=new_kv[0], v_new=new_kv[1]))
     qf = o.widen(q, qo_dtype)
     sc = scale if scale else 1.0 / np.sqrt(m.D)
     row = 0
@@ -111,6 +113,39 @@ def test_prefill_query_type_other_than_the_pool_and_host_tensors():
     m.append([a], [140])
     prefill_check(m, [a], [100], qo_dtype="f32", scale=0.2)
     prefill_check(m, [a], [140], host=True)
+
+
+@pytest.mark.parametrize("dtype,D", [("bf16", 128), ("f16", 64)])
+def test_prefill_with_the_append_in_the_same_call(dtype, D):
+    """Fresh prompts (dense forward on the caller's K/V, pages written on the side), later chunks and a prompt behind a
+    shared prefix (pages read in place), mixed in one call; the pool afterwards is what separate appends leave."""
+    m = Mirror(num_pages=120, heads=2, head_dim=D, dtype=dtype, max_seqs=8, max_pages=40, seed=31)
+    a, b, c = m.create(), m.create(), m.create()
+    prefill_check(m, [a, b], [300, 17], append=True)                     # two fresh prompts
+    m.check_tables()
+    prefill_check(m, [a, c, b], [150, 260, 1], append=True)              # a later chunk, a fresh prompt, one more token
+    m.check_tables()
+    d = m.pool.seq_fork(a, 200)
+    dm, frm, to = m.model.fork(a, 200)
+    assert d == dm
+    m.kc[to, : 200 % 16] = m.kc[frm, : 200 % 16]
+    m.vc[to, : 200 % 16] = m.vc[frm, : 200 % 16]
+    prefill_check(m, [d], [75], append=True, group=2)                    # behind a shared prefix, grouped-query
+    m.check_tables()
+    for s in (a, b, c, d):                                               # a decode sees every token
+        m.decode_check([s])
+
+
+def test_prefill_append_general_path_and_refusal():
+    m = Mirror(num_pages=12, heads=2, head_dim=64, dtype="f32", max_seqs=4, max_pages=6, seed=32)
+    a, b = m.create(), m.create()
+    prefill_check(m, [a, b], [40, 9], append=True)                       # FP32 pool: gather + dense kernels
+    prefill_check(m, [a], [20], append=True, host=True)
+    q = torch.zeros((100, 2, 64), dtype=torch.float32, device=DEV)
+    with pytest.raises(abi.AhpcError) as e:                              # the table row of b would overflow
+        m.pool.prefill([b], [100], q, k_new=q, v_new=q)
+    assert e.value.status == 3
+    m.check_tables()
 
 
 def test_prefill_head_major_buffers():
