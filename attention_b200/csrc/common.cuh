@@ -146,6 +146,9 @@ struct PagedDecodeTcLaunch {
     cudaStream_t stream;
 };
 ahpc_status launch_decode_tc(const PagedDecodeTcLaunch& a);
+// The same with the keys along the rows of the MMA tile (paged_decode_tc.cu): head_dim 128, groups of up to 16 heads.
+bool decode_tc_keys_supported(const PagedDecodeTcLaunch& a);
+ahpc_status launch_decode_tc_keys(const PagedDecodeTcLaunch& a);
 bool fa_paged_tc_supported(const PagedPrefillLaunch& a, const char** why);
 ahpc_status launch_fa_paged_tc(const PagedPrefillLaunch& a);
 

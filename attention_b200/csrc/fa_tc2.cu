@@ -54,13 +54,8 @@ constexpr int EPI_WARP0 = SOFTMAX_WARPS + 4;          // four epilogue warps (a 
 // The kernel is launched with 80 registers per thread (65536 / 768 rounded down to a multiple of 8); the issuing and
 // epilogue warpgroups then hand part of their share to the softmax warpgroups: 512 * 96 + 256 * 48 = 768 * 80.
 constexpr int SOFTMAX_REGS = 96, OTHER_REGS = 48;
-// Which of every 8 consecutive score pairs get their 2^x from poly_exp2_x2 (FMA pipe) instead of ex2 (special-
-// function unit).  Measured on B200: no pattern beats all-ex2 (the packed FP32 instructions of the cubic cost the
-// FMA pipe about as many cycles as the ex2 they replace cost the special-function unit), so the default is none.
-#ifndef AHPC_TC2_POLY
-#define AHPC_TC2_POLY 0x0
-#endif
-constexpr uint32_t POLY_PATTERN = AHPC_TC2_POLY;
+// All 2^x come from ex2 on the special-function unit.  A cubic on the FMA pipe for part of them was measured on B200 and
+// beat no mix: its packed FP32 instructions cost the FMA pipe about as many cycles as the ex2 they replace cost the other.
 
 template <int D> struct Cfg2 {
     static constexpr int SUBTILES = D / 64;                  // 64-element (128-byte) wide column blocks
@@ -92,14 +87,6 @@ struct Tc2Params {
     int* item_counter;   // zero at launch; items beyond the first gridDim.x are drawn from it
 };
 
-#ifdef AHPC_TC2_STATS
-__device__ long long g_tc2_stats[256 * 8];      // experiment builds: per CTA {cycles, items, tiles, wait s_full, wait p_free, -, wait item}
-#define STAT_T0() const long long st_t0_ = clock64()
-#define STAT_ADD(x) (x) += clock64() - st_t0_
-#else
-#define STAT_T0()
-#define STAT_ADD(x)
-#endif
 
 struct Aux2 {            // lives behind the tiles in shared memory
     uint64_t q_full[2], q_free[2], s_full[2], s_free[2], p_full[2], p_free[2], o_done, o_free;
@@ -400,15 +387,10 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         bool ok = true;
         int t_base = 0;          // key tiles of all earlier items
         int mine = 0;            // key tiles this warp has processed, over all items
-#ifdef AHPC_TC2_STATS
-        const long long st_start = clock64();
-        long long st_items = 0, st_tiles = 0, st_s = 0, st_p = 0, st_m = 0, st_i = 0;
-        (void)st_m;
-#endif
 
         for (int k = 0; ok; ++k) {
             int w;
-            { STAT_T0(); w = next_item(k, 1440, true); STAT_ADD(st_i); }
+            w = next_item(k, 1440, true);
             if (w < 0) break;
             const Item it = decode(w);
             const int row = it.q0 + r_in_tile;
@@ -418,7 +400,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (warp == 0 && lane == 0) p.redo[w] = 0;            // the epilogue warps set it when a row left P's range
 
             for (int j = g ^ first_parity; j < it.n_kv; j += 2, ++mine) {
-                { STAT_T0(); ok = wait_bounded(smem_u32(&aux->s_full[g]), mine & 1, abort_flag, p.error_word, 1300 + g); STAT_ADD(st_s); }
+                ok = wait_bounded(smem_u32(&aux->s_full[g]), mine & 1, abort_flag, p.error_word, 1300 + g);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const int k0 = j * BN + hc * 64;                                            // first key of this warp's columns
@@ -446,12 +428,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
                         const uint64_t x2 = mul2(pack_u2(sr[c][2 * e], sr[c][2 * e + 1]), scale2);
-                        uint64_t p2;
-                        if ((POLY_PATTERN >> (e & 7)) & 1u) {
-                            p2 = poly_exp2_x2(x2);
-                        } else {
-                            p2 = pack_f2(fast_exp2(__uint_as_float((uint32_t)x2)), fast_exp2(__uint_as_float((uint32_t)(x2 >> 32))));
-                        }
+                        const uint64_t p2 = pack_f2(fast_exp2(__uint_as_float((uint32_t)x2)), fast_exp2(__uint_as_float((uint32_t)(x2 >> 32))));
                         sum2[e & 3] = add2(sum2[e & 3], p2);
                         packed[c][e] = pack2<BF16>(__uint_as_float((uint32_t)p2), __uint_as_float((uint32_t)(p2 >> 32)));
                     }
@@ -459,7 +436,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 // P[g] still feeds the PV MMA of this parity's previous tile for a while after that tile's softmax ended:
                 // the probabilities wait in registers, the store comes last.
                 if (mine >= 1) {
-                    { STAT_T0(); ok = wait_bounded(smem_u32(&aux->p_free[g]), (mine - 1) & 1, abort_flag, p.error_word, 1330 + g); STAT_ADD(st_p); }
+                    ok = wait_bounded(smem_u32(&aux->p_free[g]), (mine - 1) & 1, abort_flag, p.error_word, 1330 + g);
                     if (!ok) break;
                     tc_fence_after_sync();
                 }
@@ -485,16 +462,7 @@ fa_fwd_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&aux->l_ready));     // the epilogue warps take it from here
             t_base += it.n_kv;
-#ifdef AHPC_TC2_STATS
-            ++st_items; st_tiles += it.n_kv;
-#endif
         }
-#ifdef AHPC_TC2_STATS
-        if (warp == 0 && lane == 0 && blockIdx.x < 256) {
-            long long* o = g_tc2_stats + blockIdx.x * 8;
-            o[0] = clock64() - st_start; o[1] = st_items; o[2] = st_tiles; o[3] = st_s; o[4] = st_p; o[5] = st_m; o[6] = st_i;
-        }
-#endif
     }
 
     tc_fence_before_sync();
@@ -553,9 +521,3 @@ ahpc_status launch_fa_tc2(const FaLaunch& a, int* redo_flags, int* item_counter)
 
 }  // namespace ahpc
 
-#ifdef AHPC_TC2_STATS
-extern "C" __attribute__((visibility("default"))) void ahpc_tc2_stats_read(long long* out) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, ahpc::g_tc2_stats, sizeof(long long) * 256 * 8);
-}
-#endif

@@ -91,58 +91,6 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
     return d;
 }
 
-// 2^x for two floats at once on the FMA and integer pipes instead of the special-function unit:
-// x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic (relative error 7.5e-5, below the
-// rounding step of FP16 / BF16 probabilities); n goes into the exponent field.  x is clamped at -125 so
-// that the exponent field stays positive (the cubic lies in [0.7, 1.42]); 2^-125 counts as zero.
-__device__ __forceinline__ uint64_t poly_exp2_x2(uint64_t x2) {
-    float x0 = __uint_as_float((uint32_t)x2), x1 = __uint_as_float((uint32_t)(x2 >> 32));
-    x0 = fmaxf(x0, -125.f);
-    x1 = fmaxf(x1, -125.f);
-    const uint64_t x = pack_f2(x0, x1);
-    const uint64_t magic = pack_f2(12582912.f, 12582912.f);             // 1.5 * 2^23: the sum holds n in its low mantissa bits
-    const uint64_t neg_magic = pack_f2(-12582912.f, -12582912.f);
-    const uint64_t t = add2(x, magic);
-    const uint64_t n = add2(t, neg_magic);
-    const uint64_t f = fma2(n, pack_f2(-1.f, -1.f), x);
-    uint64_t r = fma2(pack_f2(0.05517132207751274f, 0.05517132207751274f), f, pack_f2(0.24261054396629333f, 0.24261054396629333f));
-    r = fma2(r, f, pack_f2(0.6932609677314758f, 0.6932609677314758f));
-    r = fma2(r, f, pack_f2(0.9999281167984009f, 0.9999281167984009f));
-    const uint32_t lo = (uint32_t)r + ((uint32_t)t << 23);
-    const uint32_t hi = (uint32_t)(r >> 32) + ((uint32_t)(t >> 32) << 23);
-    return pack_u2(lo, hi);
-}
-
-// The same operations as volatile statements: the compiler keeps volatile asm statements in source order, which
-// lets a loop fix the interleaving of ex2 with the FMA-pipe work around it.
-__device__ __forceinline__ uint64_t fma2_v(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm volatile("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t add2_v(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm volatile("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t exp2_x2_v(uint64_t x2) {
-    uint64_t y;
-    asm volatile(
-        "{\n\t.reg .f32 lo, hi;\n\t"
-        "mov.b64 {lo, hi}, %1;\n\t"
-        "ex2.approx.ftz.f32 lo, lo;\n\t"
-        "ex2.approx.ftz.f32 hi, hi;\n\t"
-        "mov.b64 %0, {lo, hi};\n\t}"
-        : "=l"(y) : "l"(x2));
-    return y;
-}
-template <bool BF16> __device__ __forceinline__ uint32_t pack2_v(uint64_t p2) {
-    uint32_t r;
-    if (BF16) asm volatile("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.bf16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(p2));
-    else asm volatile("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.f16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(p2));
-    return r;
-}
-
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) {
     uint32_t r;

@@ -553,7 +553,8 @@ ahpc_status launch_decode(const ahpc_pool* pool, const DecodeParams& dp, cudaStr
         l.page_elems = (long long)dp.page_elems; l.num_pages = pool->cfg.num_pages; l.max_pages = dp.max_pages;
         l.part_o = dp.part_o; l.part_ml = dp.part_ml; l.split = dp.split; l.chunks = dp.max_chunks / 2;
         l.scale = dp.scale; l.device = pool->cfg.device; l.stream = st;
-        AHPC_TRY(launch_decode_tc(l));
+        if (decode_tc_keys_supported(l)) AHPC_TRY(launch_decode_tc_keys(l));
+        else AHPC_TRY(launch_decode_tc(l));
         launched = true;
     }
     if constexpr (sizeof(T) == 2) {
