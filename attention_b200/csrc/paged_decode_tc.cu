@@ -14,7 +14,8 @@
 // 4.5 TB/s for any group size up to 16, the same as the heads-along-the-rows form - about 4 us per CTA plus 1.7 us per tile
 // and SM - where the FP32 kernels, whose loads land in the registers of many small CTAs, stream at 6.3 TB/s for one head
 // per key/value head.  Neither the MMA nor the softmax work bounds it (this form has almost none); deeper rings, page ids
-// fetched per chunk instead of per tile, and one persistent CTA per SM did not move it.
+// fetched per chunk instead of per tile, one persistent CTA per SM, and asking the pages of later tiles into L2 ahead of the
+// ring (cp.async.bulk.prefetch.L2: 20 % slower) did not help.
 // 320 threads: warps 0-3 and 4-7 are two softmax groups that take an item's key
 // tiles alternately, each with its own running maximum / sum per head and its own accumulator O^T; warp 8 issues the MMAs,
 // warp 9 the copies (one bulk copy per page of keys, one TMA box per page and 128-byte column block of values).  Each group
