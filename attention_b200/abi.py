@@ -23,7 +23,7 @@ STATUS_NAMES = {
 # Every symbol include/ahpc.h declares; the CPU test-suite checks the library exports each one.
 EXPORTED_SYMBOLS = [
     "ahpc_version", "ahpc_last_error_string", "ahpc_device_count", "ahpc_get_device_info",
-    "ahpc_stream_synchronize", "ahpc_pointer_is_host",
+    "ahpc_stream_synchronize", "ahpc_pointer_is_host", "ahpc_set_workspace", "ahpc_workspace_used",
     "ahpc_fa_strides", "ahpc_fa_fwd", "ahpc_fa_workspace_bytes", "ahpc_fa_select_kernel",
     "ahpc_fa_read_error_word",
     "ahpc_pool_create", "ahpc_pool_destroy", "ahpc_pool_seq_create", "ahpc_pool_seq_destroy",
@@ -112,6 +112,9 @@ def lib() -> C.CDLL:
     L.ahpc_get_device_info.argtypes = [i32, C.POINTER(DeviceInfo)]
     L.ahpc_stream_synchronize.argtypes = [i32, vp]
     L.ahpc_pointer_is_host.argtypes = [vp]
+    L.ahpc_set_workspace.argtypes = [i32, vp, C.c_size_t]
+    L.ahpc_workspace_used.argtypes = [i32]
+    L.ahpc_workspace_used.restype = C.c_size_t
     L.ahpc_fa_strides.argtypes = [i32, i64, i64, i64, i64, C.POINTER(C.c_int64 * 4)]
     L.ahpc_fa_fwd.argtypes = [C.POINTER(FaArgs)]
     L.ahpc_fa_select_kernel.argtypes = [C.POINTER(FaArgs)]

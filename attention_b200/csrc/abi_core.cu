@@ -31,6 +31,8 @@ struct DeviceTable {
     int count = 0;
     std::map<int, cudaDeviceProp> props;
     std::map<std::pair<int, int>, std::pair<void*, size_t>> arenas;
+    struct Workspace { char* base = nullptr; size_t size = 0, used = 0; };
+    std::map<int, Workspace> workspaces;              // caller-owned device memory the arenas are carved from first
 };
 DeviceTable& table() {
     static DeviceTable t;
@@ -95,18 +97,58 @@ ahpc_status staging_buffer(int device, int slot, size_t bytes, void** out) {
     std::lock_guard<std::mutex> lock(t.mu);
     auto& arena = t.arenas[{device, slot}];
     if (arena.second < bytes) {
-        if (arena.first) {
+        DeviceTable::Workspace& ws = t.workspaces[device];
+        const bool in_ws = arena.first && ws.base && static_cast<char*>(arena.first) >= ws.base && static_cast<char*>(arena.first) < ws.base + ws.size;
+        if (arena.first && !in_ws) {
             AHPC_CUDA_OK(cudaDeviceSynchronize());
             AHPC_CUDA_OK(cudaFree(arena.first));
-            arena = {nullptr, 0};
         }
-        size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-        void* p = nullptr;
-        AHPC_CUDA_OK(cudaMalloc(&p, want));
-        arena = {p, want};
+        arena = {nullptr, 0};
+        // first from the caller's workspace (ahpc_set_workspace): a fresh 256-byte aligned piece; what an outgrown arena
+        // held there is given up until the workspace is set again
+        const size_t piece = (bytes + 255) & ~size_t(255);
+        if (ws.base && ws.used + piece <= ws.size) {
+            arena = {ws.base + ws.used, piece};
+            ws.used += piece;
+        } else {
+            size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+            void* p = nullptr;
+            AHPC_CUDA_OK(cudaMalloc(&p, want));
+            arena = {p, want};
+        }
     }
     *out = arena.first;
     return AHPC_SUCCESS;
+}
+
+ahpc_status set_workspace(int device, void* ptr, size_t bytes) {
+    DeviceTable& t = table();
+    std::lock_guard<std::mutex> lock(t.mu);
+    DeviceTable::Workspace& ws = t.workspaces[device];
+    // Arenas that live in the old workspace go with it, and the library's own are freed so that the next staging takes
+    // the new workspace first; work that still uses them must finish before.
+    AHPC_CUDA_OK(cudaDeviceSynchronize());
+    for (auto& kv : t.arenas) {
+        if (kv.first.first != device || !kv.second.first) continue;
+        char* at = static_cast<char*>(kv.second.first);
+        const bool in_old = ws.base && at >= ws.base && at < ws.base + ws.size;
+        if (!in_old && ptr) AHPC_CUDA_OK(cudaFree(kv.second.first));
+        if (in_old || ptr) kv.second = {nullptr, 0};
+    }
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(ptr), aligned = (addr + 255) & ~uintptr_t(255);
+    ws = DeviceTable::Workspace{};
+    if (ptr && bytes > aligned - addr) {
+        ws.base = reinterpret_cast<char*>(aligned);
+        ws.size = bytes - (aligned - addr);
+    }
+    return AHPC_SUCCESS;
+}
+
+size_t workspace_used(int device) {
+    DeviceTable& t = table();
+    std::lock_guard<std::mutex> lock(t.mu);
+    auto it = t.workspaces.find(device);
+    return it == t.workspaces.end() ? 0 : it->second.used;
 }
 
 }  // namespace ahpc
@@ -116,6 +158,14 @@ using namespace ahpc;
 extern "C" {
 
 const char* ahpc_version(void) { return "0.1.0"; }
+
+ahpc_status ahpc_set_workspace(int32_t device, void* ptr, size_t bytes) {
+    ScopedDevice device_guard_(device); AHPC_TRY(device_guard_.status());
+    if (ptr && is_host_pointer(ptr)) return fail(AHPC_INVALID_INPUT, "ahpc_set_workspace: the workspace must be device memory");
+    return set_workspace(device, ptr, bytes);
+}
+
+size_t ahpc_workspace_used(int32_t device) { return workspace_used(device); }
 
 const char* ahpc_last_error_string(void) { return last_error().c_str(); }
 

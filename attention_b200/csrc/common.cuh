@@ -68,6 +68,10 @@ bool is_host_pointer(const void* p);
 // host tensors.  The returned pointer stays valid until the next request for the same slot that
 // needs more room.
 ahpc_status staging_buffer(int device, int slot, size_t bytes, void** out);
+// Caller-owned device memory the staging arenas of `device` are carved from before the library allocates its own
+// (ptr = nullptr: none).  The device is synchronised when a workspace is replaced.
+ahpc_status set_workspace(int device, void* ptr, size_t bytes);
+size_t workspace_used(int device);
 
 inline size_t dtype_size(int dtype) { return dtype == AHPC_F32 ? 4 : 2; }
 inline bool dtype_valid(int dtype) { return dtype == AHPC_F32 || dtype == AHPC_F16 || dtype == AHPC_BF16; }

@@ -106,8 +106,12 @@ size_t FlashAttention::get_workspace_size(const AttentionParams& p) const {
 }
 
 void FlashAttention::set_workspace(void* workspace_ptr, size_t workspace_size) {
-    workspace_ptr_ = workspace_ptr;          // accepted and kept for interface compatibility; never consumed (as in the reference)
+    workspace_ptr_ = workspace_ptr;
     workspace_size_ = workspace_size;
+    // Device memory becomes the arena host tensors are staged through; a host buffer (what the reference's callers pass,
+    // and the reference never touches) has no use here.
+    if (!workspace_ptr || !ahpc_pointer_is_host(workspace_ptr))
+        if (ahpc_status s = ahpc_set_workspace(device_, workspace_ptr, workspace_size)) raise(s);
 }
 
 bool FlashAttention::supports_data_type(DataType t) const { return t == DataType::FLOAT32 || t == DataType::FLOAT16 || t == DataType::BFLOAT16; }

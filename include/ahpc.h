@@ -105,6 +105,15 @@ AHPC_API ahpc_status ahpc_stream_synchronize(int32_t device, void* stream);
 /* 1 if `ptr` is ordinary host memory the library would stage, 0 if the GPU can address it directly. */
 AHPC_API int32_t ahpc_pointer_is_host(const void* ptr);
 
+/* Device workspace for the library's staging of host tensors on `device`: the buffers it would
+ * otherwise cudaMalloc are carved from this caller-owned memory as long as it has room
+ * (ahpc_fa_workspace_bytes says how much a call stages).  ptr = NULL takes it away again.  The
+ * memory must stay valid until then; replacing a workspace synchronises the device.  What
+ * AttentionInterface::set_workspace (attention_interface.hpp:176-177) is for; the reference
+ * accepts a workspace and never uses it (flash_attention.cpp:176-205). */
+AHPC_API ahpc_status ahpc_set_workspace(int32_t device, void* ptr, size_t bytes);
+AHPC_API size_t ahpc_workspace_used(int32_t device);     /* bytes carved so far */
+
 /* ------------------------------------------------------------------------------------------
  * FlashAttention forward
  * Replaces launch_flash_attention_kernel (cuda_flash_attention.hpp:42-48), i.e. the body of

@@ -284,3 +284,27 @@ def test_c4_full_size_sampled_row_blocks():
         for r0 in (0, 16320, c.seq - 128):
             _check_rows(c, tq, tk, tv, out, 0, h, r0, r0 + 128)
     assert _error_word() == 0
+
+
+def test_caller_workspace_serves_the_staging_of_host_tensors():
+    """ahpc_set_workspace: host tensors are staged through caller-owned device memory while it has room."""
+    import ctypes as C
+    lib = abi.lib()
+    vals, tens = u.rounded_inputs((1, 2, 200, 64), "f32", seed=77)
+    want = o.attention_fwd(*vals, 0.125, causal=True)
+    ws = torch.empty(8 << 20, dtype=torch.uint8, device=DEV)
+    abi.check(lib.ahpc_set_workspace(0, ws.data_ptr(), ws.numel()))
+    try:
+        assert lib.ahpc_workspace_used(0) == 0
+        out = ops.flash_attention_forward(*tens, causal=True, scale=0.125, device=0)          # host tensors in, host tensor out
+        u.assert_close(u.torch_to_f32(out), want, "f32", "host tensors through a caller workspace")
+        used = lib.ahpc_workspace_used(0)
+        assert 4 * 1 * 2 * 200 * 64 * 4 <= used <= ws.numel()
+        out2 = ops.flash_attention_forward(*tens, causal=True, scale=0.125, device=0)
+        assert lib.ahpc_workspace_used(0) == used and torch.equal(out, out2)                  # the arenas are kept
+        host = torch.empty(16)
+        assert lib.ahpc_set_workspace(0, host.data_ptr(), 64) == 1                            # host memory is refused
+    finally:
+        abi.check(lib.ahpc_set_workspace(0, None, 0))
+    out3 = ops.flash_attention_forward(*tens, causal=True, scale=0.125, device=0)             # back on the library's own arenas
+    assert torch.equal(out, out3)
