@@ -54,6 +54,9 @@ constexpr int EPI_WARP0 = SOFTMAX_WARPS + 4;          // four epilogue warps (a 
 // The kernel is launched with 80 registers per thread (65536 / 768 rounded down to a multiple of 8); the issuing and
 // epilogue warpgroups then hand part of their share to the softmax warpgroups: 512 * 96 + 256 * 48 = 768 * 80.
 constexpr int SOFTMAX_REGS = 96, OTHER_REGS = 48;
+// setmaxnreg only moves registers between the warps of a CTA: the quotas must add up to what the launch gave it, or an
+// increase waits for ever.
+static_assert(SOFTMAX_WARPS * 32 * SOFTMAX_REGS + 8 * 32 * OTHER_REGS == TC2_THREADS * 80, "register quotas must add up to the CTA's allocation");
 // All 2^x come from ex2 on the special-function unit.  A cubic on the FMA pipe for part of them was measured on B200 and
 // beat no mix: its packed FP32 instructions cost the FMA pipe about as many cycles as the ex2 they replace cost the other.
 
