@@ -650,7 +650,9 @@ static ahpc_status decode_locked(const ahpc_decode_args* a, int q_heads, const v
         max_len = std::max(max_len, p->h_len[s]);
     }
     const int ps = p->cfg.page_size;
-    const bool use_tc = new_k == nullptr && tc_decode_eligible(p, q_heads, a->qo_dtype, a->split_tokens);
+    // (the tensor-core decode reads q through a tensor map, which wants a 16-byte aligned base; a host q is staged, so it is)
+    const bool use_tc = new_k == nullptr && tc_decode_eligible(p, q_heads, a->qo_dtype, a->split_tokens) &&
+                        (is_host_pointer(a->q) || reinterpret_cast<uintptr_t>(a->q) % 16 == 0);
     int split;
     if (use_tc) {
         // One CTA per (chunk, key/value head, sequence) fills an SM: long chunks, halved until the grid holds two rounds.
