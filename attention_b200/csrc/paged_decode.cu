@@ -525,7 +525,7 @@ int pick_split(const ahpc_pool* p, const int32_t* seqs, int n, int requested, in
 }
 
 // AHPC_DECODE_KERNEL=simt keeps grouped-query decodes on the FP32 kernels, =tc sends every eligible call (any group
-// size) to the tensor-core decode; unset, groups of more than 4 query heads per key/value head go there.
+// size) to the tensor-core decode; unset, groups of 3 and more query heads per key/value head go there.
 int decode_kernel_choice() {
     static const int choice = [] {
         const char* e = std::getenv("AHPC_DECODE_KERNEL");
@@ -538,7 +538,10 @@ bool tc_decode_eligible(const ahpc_pool* p, int q_heads, int qo_dtype, int reque
     const int group = q_heads / p->cfg.heads, choice = decode_kernel_choice();
     if (!fast_path(p) || qo_dtype != p->cfg.dtype || group > 128 || choice == 1) return false;
     if (requested_split > 0 && requested_split % 128 != 0) return false;
-    return choice == 2 || group > 4;        // a group of 4 runs as fast on paged_decode_gqa_kernel (measured), larger ones do not
+    // Measured (8 key/value heads, batches of 1..128 sequences of 512..16384 tokens): from 4 query heads per key/value head
+    // on the tensor-core decode is the faster one (up to 1.4x at 4, 2x at 8); a pair runs faster on paged_decode_gqa_kernel;
+    // three would run on the one-head kernel and read K/V three times.
+    return choice == 2 || group >= 3;
 }
 
 template <typename T, typename TQ>

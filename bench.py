@@ -392,7 +392,8 @@ def bench_decode(torch, dist, cfg, args, rank: int, world: int, peaks, peak_kind
                 "h2d_bytes_per_step": q.numel() * 2 + len(seqs) * 4, "d2h_bytes_per_step": q.numel() * 2, "ms_per_step": ms_e2e},
         "roofline": {"bound": "hbm", "achieved": gbs_rank, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs_rank / peaks["hbm_gbs"],
                      "traffic": NCU_TRAFFIC["paged_decode_kernel_ratio"] * by["total_unique"] if args.decode_group == 1 else None, "peak_source": peak_kind, "frac_of_nominal_8000": gbs_rank / 8000.0,
-                     "kernel": ("paged_decode_kernel" if args.decode_group == 1 else "paged_decode_gqa_kernel" if args.decode_group <= 4
+                     "kernel": ("paged_decode_kernel" if args.decode_group == 1 else "paged_decode_gqa_kernel" if args.decode_group == 2
+                                else "paged_decode_tc_kernel" if args.decode_group <= 16 and cfg.head_dim == 128
                                 else "fa_fwd_tc_kernel<MODE_DECODE>") + " (+ paged_combine_kernel in the same timed step)",
                      "bytes_per_launch": by["total_unique"]},
         "clocks": clk.summary(), "gpu_launches": 2 * args.steps,
