@@ -23,6 +23,17 @@
 // maximum in use was fixed; until then the stale maximum stays in use, which is exact because the
 // final division uses a row sum accumulated with the same maximum.
 //
+// The kernel has three modes (template parameter MODE):
+//   MODE_DENSE    K/V are dense tensors read through tensor maps (ahpc_fa_fwd; also the second pass behind fa_fwd_tc2_kernel).
+//   MODE_PREFILL  K/V live in the paged pool (pool.cuh): grid (query-tile pair, query head, sequence); the TMA warp walks the
+//                 block table and brings a key tile as 8 bulk copies of the pages' 4 KB blocks - the pool keeps them in the
+//                 unswizzled K-major operand form - and a value tile as 8 x head_dim/64 boxes; the queries are the sequence's
+//                 LAST rows for the causal rule (ahpc_paged_prefill; paged_attention.cpp:132-174, 596-680 of the reference).
+//   MODE_DECODE   one query token per sequence, grouped-query attention: the query heads that share a key/value head are the
+//                 rows of the tile, the CTA's two tile slots take the key tiles of its chunk alternately and leave two
+//                 partials for paged_combine_kernel (ahpc_paged_decode for groups the keys-along-the-rows kernel of
+//                 paged_decode_tc.cu does not take).
+//
 // Every wait in this kernel is bounded: when a barrier does not complete within the limit the
 // waiting thread records a code in a global error word, raises a CTA-wide abort flag, and every
 // role leaves its loop; tensor memory is then released and the kernel returns.
