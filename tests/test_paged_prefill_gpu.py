@@ -66,6 +66,23 @@ def test_prefill_over_pages_ragged_batch(dtype, D):
     prefill_check(m, [seqs[3]], [0])                                       # nothing to do
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_prefill_equal_query_runs_and_extreme_scores(D):
+    """The same number of query tokens for every listed sequence, behind contexts of different lengths; and scores far
+    beyond what probabilities without a row maximum could hold (the kernel's rescaling softmax copes)."""
+    m = Mirror(num_pages=140, heads=2, head_dim=D, dtype="bf16", max_seqs=8, max_pages=40, seed=41)
+    lens = [300, 129, 512, 200, 1]
+    seqs = [m.create() for _ in lens]
+    m.append(seqs, lens)
+    prefill_check(m, seqs[:4], [100] * 4)                                 # chunks at the end of contexts of different lengths
+    prefill_check(m, seqs[:4], [129] * 4, causal=False)
+    prefill_check(m, [seqs[2]], [512])                                    # a whole prompt, four query tiles
+    prefill_check(m, [seqs[4], seqs[0]], [1, 1])                          # one token each
+    prefill_check(m, seqs[:3], [120] * 3, group=2)
+    prefill_check(m, seqs[:4], [100] * 4, scale=4.0)
+    prefill_check(m, seqs[:2], [64] * 2, scale=6.0, causal=False)
+
+
 @pytest.mark.parametrize("group", [2, 4])
 def test_prefill_grouped_query_attention(group):
     m = Mirror(num_pages=80, heads=2, head_dim=128, dtype="bf16", max_seqs=4, max_pages=40, seed=12)
